@@ -1,0 +1,74 @@
+"""ctypes binding of libffnk.so, the C-ABI library that holds every CUDA kernel.
+
+There is no fallback: if the library is missing or a call is rejected, an exception
+is raised.  Nothing in this package computes on the CPU or through another library.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_int, c_int32, c_int64, c_void_p, POINTER
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libffnk.so")
+
+_I32P = POINTER(c_int32)
+
+# name -> (restype, argtypes); mirrors include/ffnk.h declaration by declaration
+SIGNATURES = {
+    "ffnk_version": (c_int, []),
+    "ffnk_route_capacity": (c_int64, [c_int64]),
+    "ffnk_route_workspace_bytes": (c_int64, [c_int64]),
+    "ffnk_route": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ffnk_linear_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                                c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ffnk_linear_bwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                c_int64, c_void_p, c_void_p]),
+    "ffnk_ffn_gateup": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int64,
+                                c_void_p, c_void_p]),
+    "ffnk_ffn_down": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                              c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ffnk_decode_max_tokens": (c_int, []),
+    "ffnk_ffn_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
+                                c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ffnk_read_status": (c_int, [c_void_p, c_int, c_void_p]),
+    "ffnk_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
+    "ffnk_status_string": (c_char_p, [c_int]),
+}
+
+_lib = None
+
+
+class FfnkError(RuntimeError):
+    """A call into libffnk.so was rejected or reported a device-side error."""
+
+    def __init__(self, where: str, code: int):
+        self.code = code
+        msg = lib().ffnk_status_string(code).decode() if _lib is not None else "?"
+        super().__init__(f"{where}: {msg} (code {code})")
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: the CUDA kernels have not been built. "
+                "Run `python -m ffn_kernel_b200.build` (needs nvcc); there is no CPU or Triton fallback.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name, None)
+            if fn is None:   # TEMP while kernels are being brought up
+                continue
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(where: str, code: int) -> None:
+    if code != 0:
+        raise FfnkError(where, code)

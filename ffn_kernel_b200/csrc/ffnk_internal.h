@@ -1,0 +1,33 @@
+// Host-side helpers shared by the translation units of libffnk: error mapping, TMA tensor-map
+// construction through the driver entry point (no link-time dependency on libcuda).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ffnk.h"
+
+namespace ffnk {
+
+// CUDA runtime errors are reported as -(1000 + cudaError_t) so that they cannot be confused with
+// argument errors (small negatives) or device status codes (small positives).
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? 0 : -(1000 + static_cast<int>(e)); }
+
+// Number of SMs / compute capability of the current device (cached per device).
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+  int smem_optin = 0;
+};
+const DeviceInfo& device_info();
+
+// 2-D bf16 tensor map with 128-byte swizzle.
+//   inner/outer : extents in elements (inner is contiguous)
+//   row_stride  : elements between consecutive outer indices
+//   box_inner/box_outer : tile extents; box_inner * 2 bytes must be 128
+// Returns 0 or FFNK_ERR_*.
+int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride,
+                       uint32_t box_inner, uint32_t box_outer);
+
+}  // namespace ffnk

@@ -1,0 +1,188 @@
+// Routing: boolean token mask -> per-modality compacted row-index lists.
+//
+// Replaces the reference's per-tile "is this tile all visual / all text / mixed" test
+// (ffn_kernel/linear.py:132-149, ffn_kernel/ffn.py:72-99): once the rows of each modality are
+// known as a list, every GEMM tile multiplies one modality's rows by one modality's weights.
+//
+//   perm[0 .. Mv)            = ascending indices of tokens with mask != 0   (visual)
+//   perm[cap .. cap + Mt)    = ascending indices of tokens with mask == 0   (text)
+//   counts[0] = Mv, counts[1] = Mt, counts[2] = cap, counts[3] = M
+//
+// Integer work, bit-exact with nonzero(mask) / nonzero(~mask).  One pass over the mask: a
+// chained scan with decoupled look-back.  Tiles are handed out by an atomic ticket so that a
+// tile's predecessors have always started; the look-back spin is bounded all the same.
+//
+// Algorithmic traffic: 1 byte read + 4 bytes written per token.
+#include "ffnk_internal.h"
+#include "ptx.cuh"
+
+namespace ffnk {
+
+constexpr int kRouteThreads = 256;
+constexpr int kRoutePerThread = 16;                             // one 128-bit load of mask bytes
+constexpr int kRouteTile = kRouteThreads * kRoutePerThread;     // 4096 tokens per tile
+
+// tile state word: [31:30] flag (0 = nothing, 1 = tile aggregate, 2 = inclusive prefix), [29:0] visual count
+constexpr uint32_t kFlagAgg = 1u << 30;
+constexpr uint32_t kFlagInc = 2u << 30;
+constexpr uint32_t kValMask = (1u << 30) - 1;
+
+__global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __restrict__ mask, int M, int cap,
+                                                              int* __restrict__ perm, int* __restrict__ counts,
+                                                              uint32_t* __restrict__ ws,  // [0] ticket, [1..] tile state
+                                                              int* __restrict__ status) {
+  __shared__ int s_list[kRouteTile];  // visual indices from the front, text indices after them
+  __shared__ int s_warp[kRouteThreads / 32];
+  __shared__ int s_tile, s_excl, s_ok;
+
+  const int tid = threadIdx.x;
+  if (tid == 0) s_tile = static_cast<int>(atomicAdd(&ws[0], 1u));
+  __syncthreads();
+  const int tile = s_tile;
+  const int num_tiles = (M + kRouteTile - 1) / kRouteTile;
+  volatile uint32_t* state = ws + 1;
+
+  const int base = tile * kRouteTile + tid * kRoutePerThread;
+  // 16 mask bytes of this thread
+  uint32_t w[4] = {0, 0, 0, 0};
+  int valid = M - base;
+  valid = valid < 0 ? 0 : (valid > kRoutePerThread ? kRoutePerThread : valid);
+  if (valid == kRoutePerThread && ((reinterpret_cast<uintptr_t>(mask) & 15) == 0)) {
+    const uint4 v = *reinterpret_cast<const uint4*>(mask + base);
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+  } else {
+    for (int i = 0; i < valid; ++i) w[i >> 2] |= static_cast<uint32_t>(mask[base + i]) << (8 * (i & 3));
+  }
+  // bit i of `bits` = token base+i is visual
+  uint32_t bits = 0;
+#pragma unroll
+  for (int i = 0; i < kRoutePerThread; ++i) bits |= (((w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0 ? 1u : 0u) << i;
+  const int nv = __popc(bits);
+
+  // block-wide exclusive scan of nv
+  int incl = nv;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if ((tid & 31) >= o) incl += n;
+  }
+  if ((tid & 31) == 31) s_warp[tid >> 5] = incl;
+  __syncthreads();
+  int warp_off = 0, tile_v = 0;
+#pragma unroll
+  for (int i = 0; i < kRouteThreads / 32; ++i) {
+    const int c = s_warp[i];
+    if (i < (tid >> 5)) warp_off += c;
+    tile_v += c;
+  }
+  const int ev = warp_off + incl - nv;                 // visual tokens before this thread, in tile
+  const int tile_len = min(kRouteTile, M - tile * kRouteTile);
+  const int tile_t = tile_len - tile_v;
+
+  // publish the tile aggregate, then look back for the exclusive prefix
+  if (tid == 0) {
+    if (tile == 0) {
+      state[0] = kFlagInc | static_cast<uint32_t>(tile_v);
+      s_excl = 0;
+      s_ok = 1;
+    } else {
+      state[tile] = kFlagAgg | static_cast<uint32_t>(tile_v);
+    }
+  }
+  if (tile > 0 && tid < 32) {
+    // warp 0 walks back 32 tiles at a time
+    int excl = 0, ok = 1;
+    int look = tile - 1;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      const int idx = look - static_cast<int>(tid);
+      uint32_t s = 2u << 30;  // before tile 0: an inclusive prefix of 0
+      if (idx >= 0) s = state[idx];
+      // wait until every inspected tile has published something (all branches warp-uniform)
+      uint32_t polls = 0;
+      while (true) {
+        const bool pending = idx >= 0 && (s >> 30) == 0;
+        if (!__any_sync(0xFFFFFFFFu, pending)) break;
+        if (pending) s = state[idx];
+        ++polls;
+        const bool expired = (polls & 63u) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs;
+        if (__any_sync(0xFFFFFFFFu, expired)) { ok = 0; break; }
+      }
+      if (!ok) break;
+      const uint32_t inc_ballot = __ballot_sync(0xFFFFFFFFu, (s >> 30) == 2);
+      // lanes nearer than the first inclusive prefix contribute their aggregate; that lane its prefix
+      const int first_inc = inc_ballot ? (__ffs(inc_ballot) - 1) : 32;
+      int contrib = (static_cast<int>(tid) <= first_inc) ? static_cast<int>(s & kValMask) : 0;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xFFFFFFFFu, contrib, o);
+      excl += contrib;
+      if (inc_ballot) break;
+      look -= 32;
+    }
+    if (tid == 0) {
+      s_excl = excl;
+      s_ok = ok;
+      if (ok) state[tile] = kFlagInc | static_cast<uint32_t>(excl + tile_v);
+      else atomicCAS(status, 0, ST_TIMEOUT_SCAN);
+    }
+  }
+
+  // compact inside the tile: visual indices to s_list[0..tile_v), text to s_list[tile_v..tile_len)
+  {
+    int pv = ev, pt = tile_v + (tid * kRoutePerThread - ev);
+#pragma unroll
+    for (int i = 0; i < kRoutePerThread; ++i) {
+      if (i < valid) {
+        if ((bits >> i) & 1u) s_list[pv++] = base + i;
+        else s_list[pt++] = base + i;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int pre_v = s_excl;
+  const int pre_t = tile * kRouteTile - pre_v;
+  for (int i = tid; i < tile_v; i += kRouteThreads) perm[pre_v + i] = s_list[i];
+  for (int i = tid; i < tile_t; i += kRouteThreads) perm[cap + pre_t + i] = s_list[tile_v + i];
+  if (tile == num_tiles - 1 && tid == 0) {
+    counts[0] = pre_v + tile_v;
+    counts[1] = M - (pre_v + tile_v);
+    counts[2] = cap;
+    counts[3] = M;
+  }
+}
+
+__global__ void route_empty_kernel(int* counts, int cap) {
+  counts[0] = 0; counts[1] = 0; counts[2] = cap; counts[3] = 0;
+}
+
+}  // namespace ffnk
+
+using namespace ffnk;
+
+extern "C" int64_t ffnk_route_capacity(int64_t M) { return ((M + 127) / 128) * 128; }
+
+extern "C" int64_t ffnk_route_workspace_bytes(int64_t M) {
+  const int64_t tiles = (M + kRouteTile - 1) / kRouteTile;
+  return (tiles + 1) * static_cast<int64_t>(sizeof(uint32_t));
+}
+
+extern "C" int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* counts, void* workspace,
+                          int32_t* status, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || M >= (1ll << 30)) return FFNK_ERR_SHAPE;
+  if (!counts || !status) return FFNK_ERR_NULL;
+  const int cap = static_cast<int>(ffnk_route_capacity(M));
+  if (M == 0) {
+    route_empty_kernel<<<1, 1, 0, stream>>>(counts, cap);
+    return cuda_status(cudaGetLastError());
+  }
+  if (!mask || !perm || !workspace) return FFNK_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(perm) & 15) return FFNK_ERR_ALIGN;
+  const int tiles = static_cast<int>((M + kRouteTile - 1) / kRouteTile);
+  cudaError_t e = cudaMemsetAsync(workspace, 0, ffnk_route_workspace_bytes(M), stream);
+  if (e != cudaSuccess) return cuda_status(e);
+  route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,
+                                                    counts, static_cast<uint32_t*>(workspace), status);
+  return cuda_status(cudaGetLastError());
+}

@@ -1,0 +1,783 @@
+// Routed grouped GEMM for sm_100a: the forward GEMMs of MaskedLinear and MaskedFFN and the
+// dx GEMM of MaskedLinear backward.
+//
+// The token rows of each modality are a compacted list (route.cu).  A CTA tile is 128 routed
+// rows of ONE modality times 256 accumulator columns, so a tile multiplies by exactly one
+// weight set -- the reference instead tiles tokens in natural order and, for a tile holding
+// both modalities, computes both products and selects (ffn_kernel/linear.py:142-149,
+// ffn_kernel/ffn.py:86-99).
+//
+// Structure of one persistent CTA (192 threads, one CTA per SM):
+//   warp 0      producer: TMA.  A rows are fetched with gather4 (four arbitrary rows of 128 B
+//               per instruction, lane l of the warp owns rows 4l..4l+3 of the tile) or, when A
+//               is already in routed order, with one tiled load.  B comes from the weight's own
+//               storage, K-major ([N,K], the nn.Linear.weight.T view) or MN-major ([K,N]).
+//   warp 1      issues tcgen05.mma (bf16 x bf16 -> fp32 in TMEM), 128x256x16 per instruction,
+//               four per 64-wide k-step; owns the TMEM allocation.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, convert (optionally SiLU(t1)*t3), store
+//               bf16 rows to their destination (token order via the list, or routed order).
+// Shared-memory stages are handed between producer and MMA with full/empty mbarriers; the
+// accumulator is double buffered in TMEM (2 x 256 columns) so the epilogue of tile i runs
+// under the main loop of tile i+1.
+#include <cuda_bf16.h>
+
+#include "ffnk_internal.h"
+#include "ptx.cuh"
+
+namespace ffnk {
+
+constexpr int BM = 128;                 // routed rows per tile (UMMA M)
+constexpr int BN = 256;                 // accumulator columns per tile (UMMA N)
+constexpr int BK = 64;                  // k-step: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;    // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;    // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+enum { A_GATHER = 0, A_ROUTED = 1 };
+enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+enum { OUT_SCATTER = 0, OUT_ROUTED = 1 };
+
+struct GemmParams {
+  const int* perm;      // routing lists
+  const int* counts;    // {Mv, Mt, cap, M}
+  __nv_bfloat16* out;
+  int64_t ldo;          // elements
+  int n_out;            // valid output columns
+  int k_len;            // contraction length
+  int pad_row;          // row index fetched for the padding rows of a tile (>= M: zero fill)
+  int group_m;          // m-tiles per super-tile of the tile order
+  int* status;
+};
+
+struct TileCoord {
+  int mt, nt;           // m-tile over [visual tiles | text tiles], n-tile
+  int row0;             // first row of the tile inside its modality's list
+  int rows;             // valid rows in the tile (1..128)
+  int list_off;         // offset of the modality's list inside perm
+  bool text;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(int t, int tiles_v, int m_tiles, int n_tiles, int group_m, int Mv,
+                                                 int Mt, int cap) {
+  TileCoord c;
+  const int per_super = group_m * n_tiles;
+  const int st = t / per_super;
+  const int r = t - st * per_super;
+  const int m0 = st * group_m;
+  const int gm = min(group_m, m_tiles - m0);
+  c.nt = r / gm;
+  c.mt = m0 + (r - c.nt * gm);
+  c.text = c.mt >= tiles_v;
+  const int lt = c.text ? c.mt - tiles_v : c.mt;
+  c.row0 = lt * BM;
+  const int cnt = c.text ? Mt : Mv;
+  c.rows = min(BM, cnt - c.row0);
+  c.list_off = c.text ? cap : 0;
+  return c;
+}
+
+__device__ __forceinline__ void report(int* status, int code) {
+  if (status) atomicCAS(status, 0, code);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float silu_mul(float t1, float t3) {
+  // t1 * sigmoid(t1) * t3 (ffn_kernel/ffn.py:107), in fp32
+  return t1 * __frcp_rn(1.0f + __expf(-t1)) * t3;
+}
+
+template <int A_MODE, int EPI, int OUT_MODE, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBv0,
+                   const __grid_constant__ CUtensorMap tmBv1, const __grid_constant__ CUtensorMap tmBt0,
+                   const __grid_constant__ CUtensorMap tmBt1, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;   // accumulator ready for the epilogue   [2]
+  uint64_t* tempty = tfull + 2;       // accumulator drained by the epilogue  [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmBv0);
+    tma_prefetch_desc(&tmBv1);
+    tma_prefetch_desc(&tmBt0);
+    tma_prefetch_desc(&tmBt1);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int Mv = p.counts[0], Mt = p.counts[1], cap = p.counts[2];
+  const int tiles_v = (Mv + BM - 1) / BM;
+  const int m_tiles = tiles_v + (Mt + BM - 1) / BM;
+  constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const int n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_steps = (p.k_len + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    int stage = 0;
+    uint32_t phase = 0;
+    int issued = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const TileCoord tc = decode_tile(t, tiles_v, m_tiles, n_tiles, p.group_m, Mv, Mt, cap);
+      int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
+      if constexpr (A_MODE == A_GATHER) {
+        const int lr = 4 * lane;  // first of this lane's four rows
+        if (lr < tc.rows) {
+          const int4 v = *reinterpret_cast<const int4*>(p.perm + tc.list_off + tc.row0 + lr);
+          r0 = v.x;
+          if (lr + 1 < tc.rows) r1 = v.y;
+          if (lr + 2 < tc.rows) r2 = v.z;
+          if (lr + 3 < tc.rows) r3 = v.w;
+        }
+      }
+      const CUtensorMap* mB0 = tc.text ? &tmBt0 : &tmBv0;
+      const CUtensorMap* mB1 = tc.text ? &tmBt1 : &tmBv1;
+      for (int ks = 0; ks < k_steps; ++ks) {
+        int w = 1;
+        if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
+        w = __shfl_sync(0xFFFFFFFFu, w, 0);
+        if (!w) {
+          if (lane == 0) report(p.status, ST_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        uint8_t* sa = smem + stage * STAGE_BYTES;
+        uint8_t* sb = sa + A_BYTES;
+        if (lane == 0) mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+        __syncwarp();
+        const int kx = ks * BK;
+        if constexpr (A_MODE == A_GATHER) {
+          tma_gather4(sa + lane * 512, &tmA, &full[stage], kx, r0, r1, r2, r3);
+        } else {
+          if (lane == 0) tma_load_2d(sa, &tmA, &full[stage], kx, tc.mt * BM);
+        }
+        if (lane == 0) {
+          if constexpr (!B_MN) {
+            // K-major weights: two boxes of 128 weight rows x 64 k
+            const int n0 = (EPI == EPI_SWIGLU) ? tc.nt * (BN / 2) : tc.nt * BN;
+            const int n1 = (EPI == EPI_SWIGLU) ? n0 : n0 + BN / 2;
+            tma_load_2d(sb, mB0, &full[stage], kx, n0);
+            tma_load_2d(sb + B_BYTES / 2, mB1, &full[stage], kx, n1);
+          } else {
+            // MN-major weights: four boxes of 64 k rows x 64 output columns
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const CUtensorMap* m = (EPI == EPI_SWIGLU && j >= 2) ? mB1 : mB0;
+              const int n = (EPI == EPI_SWIGLU) ? tc.nt * (BN / 2) + (j & 1) * 64 : tc.nt * BN + j * 64;
+              tma_load_2d(sb + j * (B_BYTES / 4), m, &full[stage], n, kx);
+            }
+          }
+        }
+        ++issued;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (*abort_flag && lane == 0) {
+      // let the copies already issued land before the CTA gives its shared memory back
+      int s = stage;
+      uint32_t ph = phase;
+      const int n = issued < STAGES ? issued : STAGES;
+      for (int i = 0; i < n; ++i) {
+        if (--s < 0) { s = STAGES - 1; ph ^= 1; }
+        int dummy = 0;
+        mbar_wait(&full[s], ph, &dummy, 1000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+          report(p.status, ST_TIMEOUT_MMA_TMEM);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            report(p.status, ST_TIMEOUT_MMA_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = umma_smem_desc(a_addr + kk * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc(b_addr + kk * (UMMA_K * 128), B_BYTES / 4, 1024)
+                                     : umma_smem_desc(b_addr + kk * (UMMA_K * 2), 16, 1024);
+            umma_bf16<1>(tmem_d, da, db, idesc, (ks | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;       // row of the tile held by this thread
+    int it = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      const TileCoord tc = decode_tile(t, tiles_v, m_tiles, n_tiles, p.group_m, Mv, Mt, cap);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const bool valid = row < tc.rows;
+      int64_t dst_row = 0;
+      if (valid) {
+        if constexpr (OUT_MODE == OUT_SCATTER) dst_row = p.perm[tc.list_off + tc.row0 + row];
+        else dst_row = static_cast<int64_t>(tc.mt) * BM + row;
+      }
+      int w = 1;
+      if (lane == 0) w = mbar_wait(&tfull[acc], acc_phase, abort_flag) ? 1 : 0;
+      w = __shfl_sync(0xFFFFFFFFu, w, 0);
+      if (!w) {
+        if (lane == 0) report(p.status, ST_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      __nv_bfloat16* out_row = p.out + dst_row * p.ldo;
+      if constexpr (EPI == EPI_STORE) {
+        const int n_base = tc.nt * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          const int n0 = n_base + c * 32;
+          if (valid && n0 < p.n_out) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n0 + j * 8 < p.n_out) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
+                o.y = pack_bf16(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
+                o.z = pack_bf16(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
+                o.w = pack_bf16(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
+                *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
+              }
+            }
+          }
+        }
+      } else {
+        const int n_base = tc.nt * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + c * 32, g);            // gate  (t1)
+          tmem_ld_32x32(taddr + BN / 2 + c * 32, u);   // up    (t3)
+          tmem_ld_wait();
+          const int n0 = n_base + c * 32;
+          if (valid && n0 < p.n_out) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n0 + j * 8 < p.n_out) {
+                float h[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  h[e] = silu_mul(__uint_as_float(g[j * 8 + e]), __uint_as_float(u[j * 8 + e]));
+                uint4 o;
+                o.x = pack_bf16(h[0], h[1]);
+                o.y = pack_bf16(h[2], h[3]);
+                o.z = pack_bf16(h[4], h[5]);
+                o.w = pack_bf16(h[6], h[7]);
+                *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// Weight-gradient GEMM of MaskedLinear backward (replaces _masked_matmul_bwd_db,
+// ffn_kernel/linear.py:329-415):   out_g[p, q] = sum over rows r of modality g of P[r, p] * Q[r, q]
+// P and Q are the two row-major token matrices (activations and upstream gradient, in the
+// order that makes `out` match the weight's storage).  The contraction runs over the
+// modality's row list, so both operands are MN-major in shared memory: a k-step is 64 list
+// rows, each contributing one 128-byte row per 64-column block, fetched with gather4.  Rows
+// past the end of the list are fetched from an out-of-range row index and arrive as zeros.
+// The reference streams every token through every tile and zeroes the other modality's rows;
+// here a tile only ever touches its own modality's rows.
+// -------------------------------------------------------------------------------------------
+struct WgradParams {
+  const int* perm;
+  const int* counts;
+  __nv_bfloat16* out_v;
+  __nv_bfloat16* out_t;
+  int64_t ldo;
+  int p_dim;      // output rows    (columns of P)
+  int q_dim;      // output columns (columns of Q)
+  int pad_row;
+  int* status;
+};
+
+struct WgradTile {
+  int pt, qt, cnt, list_off;
+  bool text;
+};
+
+__device__ __forceinline__ WgradTile decode_wgrad_tile(int t, int p_tiles, int q_tiles, int Mv, int Mt, int cap) {
+  WgradTile w;
+  const int per_group = p_tiles * q_tiles;
+  const int gsel = t / per_group;
+  const int r = t - gsel * per_group;
+  // the modality with more rows goes first so that the long tiles do not end up in the tail
+  const bool text_first = Mt > Mv;
+  w.text = (gsel == 0) ? text_first : !text_first;
+  w.qt = r / p_tiles;
+  w.pt = r - w.qt * p_tiles;
+  w.cnt = w.text ? Mt : Mv;
+  w.list_off = w.text ? cap : 0;
+  return w;
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const WgradParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmP);
+    tma_prefetch_desc(&tmQ);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int Mv = p.counts[0], Mt = p.counts[1], cap = p.counts[2];
+  const int p_tiles = (p.p_dim + BM - 1) / BM;
+  const int q_tiles = (p.q_dim + BN - 1) / BN;
+  const int total_tiles = 2 * p_tiles * q_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    int stage = 0;
+    uint32_t phase = 0;
+    int issued = 0;
+    bool ok = true;
+    const int gi = lane & 15;     // which group of four list rows inside the k-step
+    const int half = lane >> 4;   // which 64-column block (of a pair)
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const WgradTile wt = decode_wgrad_tile(t, p_tiles, q_tiles, Mv, Mt, cap);
+      if (wt.cnt == 0) continue;
+      const int k_steps = (wt.cnt + BK - 1) / BK;
+      const int* list = p.perm + wt.list_off;
+      for (int ks = 0; ks < k_steps; ++ks) {
+        const int lr = ks * BK + 4 * gi;
+        int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
+        if (lr < wt.cnt) {
+          const int4 v = *reinterpret_cast<const int4*>(list + lr);
+          r0 = v.x;
+          if (lr + 1 < wt.cnt) r1 = v.y;
+          if (lr + 2 < wt.cnt) r2 = v.z;
+          if (lr + 3 < wt.cnt) r3 = v.w;
+        }
+        int w = 1;
+        if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
+        w = __shfl_sync(0xFFFFFFFFu, w, 0);
+        if (!w) {
+          if (lane == 0) report(p.status, ST_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        uint8_t* sp = smem + stage * STAGE_BYTES;
+        uint8_t* sq = sp + A_BYTES;
+        if (lane == 0) mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+        __syncwarp();
+        // P: two 64-column blocks; Q: four.  Block b lives at b * 8 KiB, list row j at j * 128 B.
+        tma_gather4(sp + half * 8192 + gi * 512, &tmP, &full[stage], wt.pt * BM + half * 64, r0, r1, r2, r3);
+        tma_gather4(sq + half * 8192 + gi * 512, &tmQ, &full[stage], wt.qt * BN + half * 64, r0, r1, r2, r3);
+        tma_gather4(sq + (2 + half) * 8192 + gi * 512, &tmQ, &full[stage], wt.qt * BN + (2 + half) * 64, r0, r1, r2,
+                    r3);
+        ++issued;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (*abort_flag && lane == 0) {
+      int s = stage;
+      uint32_t ph = phase;
+      const int n = issued < STAGES ? issued : STAGES;
+      for (int i = 0; i < n; ++i) {
+        if (--s < 0) { s = STAGES - 1; ph ^= 1; }
+        int dummy = 0;
+        mbar_wait(&full[s], ph, &dummy, 1000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, true, true);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const WgradTile wt = decode_wgrad_tile(t, p_tiles, q_tiles, Mv, Mt, cap);
+        if (wt.cnt == 0) continue;
+        const int k_steps = (wt.cnt + BK - 1) / BK;
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+          report(p.status, ST_TIMEOUT_MMA_TMEM);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            report(p.status, ST_TIMEOUT_MMA_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t p_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t q_addr = p_addr + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t dp = umma_smem_desc(p_addr + kk * (UMMA_K * 128), 8192, 1024);
+            const uint64_t dq = umma_smem_desc(q_addr + kk * (UMMA_K * 128), 8192, 1024);
+            umma_bf16<1>(tmem_d, dp, dq, idesc, (ks | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    int it = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const WgradTile wt = decode_wgrad_tile(t, p_tiles, q_tiles, Mv, Mt, cap);
+      const int prow = wt.pt * BM + row;
+      const bool valid = prow < p.p_dim;
+      __nv_bfloat16* out_row = (wt.text ? p.out_t : p.out_v) + static_cast<int64_t>(prow) * p.ldo;
+      const int q_base = wt.qt * BN;
+      if (wt.cnt == 0) {
+        // a modality without tokens has a zero gradient
+        if (valid) {
+          for (int c = 0; c < BN; c += 8)
+            if (q_base + c < p.q_dim) *reinterpret_cast<uint4*>(out_row + q_base + c) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
+      int w = 1;
+      if (lane == 0) w = mbar_wait(&tfull[acc], acc_phase, abort_flag) ? 1 : 0;
+      w = __shfl_sync(0xFFFFFFFFu, w, 0);
+      if (!w) {
+        if (lane == 0) report(p.status, ST_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int n0 = q_base + c * 32;
+        if (valid && n0 < p.q_dim) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (n0 + j * 8 < p.q_dim) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
+              o.y = pack_bf16(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
+              o.z = pack_bf16(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
+              o.w = pack_bf16(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
+              *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// host side
+// -------------------------------------------------------------------------------------------
+struct WeightView {
+  const void* base;
+  int64_t stride_k, stride_n;  // elements
+  int64_t K, N;                // logical [K, N]
+};
+
+// Tensor map over one weight for the B operand.  K-major: storage rows are output columns.
+static int weight_map(CUtensorMap* m, const WeightView& w, bool* mn_major) {
+  if (w.stride_k == 1 && (w.stride_n >= w.K || w.N == 1)) {
+    *mn_major = false;
+    return make_tensor_map_2d(m, w.base, w.K, w.N, w.stride_n, BK, BN / 2);
+  }
+  if (w.stride_n == 1 && (w.stride_k >= w.N || w.K == 1)) {
+    *mn_major = true;
+    return make_tensor_map_2d(m, w.base, w.N, w.K, w.stride_k, 64, BK);
+  }
+  return FFNK_ERR_LAYOUT;
+}
+
+static int pick_group_m(int64_t k_len) {
+  // keep one super-tile of A rows (group_m x 128 rows x K) near 32 MiB so that it stays in L2
+  // while the weights stream past it
+  int64_t g = (32ll << 20) / (BM * k_len * 2);
+  if (g < 4) g = 4;
+  if (g > 64) g = 64;
+  return static_cast<int>(g);
+}
+
+template <int A_MODE, int EPI, int OUT_MODE>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap (&tmB)[4], bool b_mn, const GemmParams& p,
+                       int64_t m_tiles_max, cudaStream_t stream) {
+  const DeviceInfo& dev = device_info();
+  if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
+  constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const int64_t n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
+  int64_t grid = m_tiles_max * n_tiles;
+  if (grid > dev.sm_count) grid = dev.sm_count;
+  if (grid < 1) grid = 1;
+  auto go = [&](auto kernel) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (e != cudaSuccess) return cuda_status(e);
+    kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
+    return cuda_status(cudaGetLastError());
+  };
+  return b_mn ? go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, true>)
+              : go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false>);
+}
+
+static bool bad_dim(int64_t v) { return v < 8 || (v & 7) || v >= (1ll << 30); }
+
+}  // namespace ffnk
+
+using namespace ffnk;
+
+extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const void* b2, int64_t b_stride_k,
+                               int64_t b_stride_n, const int32_t* perm, const int32_t* counts, void* c, int64_t ldc,
+                               int64_t M, int64_t N, int64_t K, int32_t* status, void* stream) {
+  if (M == 0) return 0;
+  if (!a || !b1 || !b2 || !perm || !counts || !c) return FFNK_ERR_NULL;
+  if (M < 0 || M >= (1ll << 30) || bad_dim(N) || bad_dim(K)) return FFNK_ERR_SHAPE;
+  if ((lda & 7) || (ldc & 7) || lda < K || ldc < N || (reinterpret_cast<uintptr_t>(c) & 15)) return FFNK_ERR_ALIGN;
+  CUtensorMap tmA, tmB[4];
+  int r = make_tensor_map_2d(&tmA, a, K, M, lda, BK, 1);
+  if (r) return r;
+  bool mn1 = false, mn2 = false;
+  if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_k, b_stride_n, K, N}, &mn1))) return r;
+  if ((r = weight_map(&tmB[2], WeightView{b2, b_stride_k, b_stride_n, K, N}, &mn2))) return r;
+  tmB[1] = tmB[0];
+  tmB[3] = tmB[2];
+  GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(c), ldc, static_cast<int>(N), static_cast<int>(K),
+               static_cast<int>(M), pick_group_m(K), status};
+  return launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1,
+                                                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1,
+                               const void* u3, int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm,
+                               const int32_t* counts, void* out, int64_t ldo, int routed_out, int64_t M, int64_t d,
+                               int64_t h, int32_t* status, void* stream) {
+  if (M == 0) return 0;
+  if (!x || !w1 || !w3 || !u1 || !u3 || !perm || !counts || !out) return FFNK_ERR_NULL;
+  if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
+  if ((ldx & 7) || (ldo & 7) || ldx < d || ldo < h || (reinterpret_cast<uintptr_t>(out) & 15)) return FFNK_ERR_ALIGN;
+  CUtensorMap tmA, tmB[4];
+  int r = make_tensor_map_2d(&tmA, x, d, M, ldx, BK, 1);
+  if (r) return r;
+  bool mn = false, mn_i = false;
+  const void* ws[4] = {w1, w3, u1, u3};
+  for (int i = 0; i < 4; ++i) {
+    if ((r = weight_map(&tmB[i], WeightView{ws[i], w_stride_k, w_stride_n, d, h}, &mn_i))) return r;
+    mn = mn_i;
+  }
+  GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(out), ldo, static_cast<int>(h), static_cast<int>(d),
+               static_cast<int>(M), pick_group_m(d), status};
+  const int64_t mt = (M + BM - 1) / BM + 1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return routed_out ? launch_gemm<A_GATHER, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, mt, s)
+                    : launch_gemm<A_GATHER, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, mt, s);
+}
+
+extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
+                             int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy,
+                             int64_t M, int64_t d, int64_t h, int32_t* status, void* stream) {
+  if (M == 0) return 0;
+  if (!inter || !w2 || !u2 || !perm || !counts || !y) return FFNK_ERR_NULL;
+  if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
+  if ((ldi & 7) || (ldy & 7) || ldi < h || ldy < d || (reinterpret_cast<uintptr_t>(y) & 15)) return FFNK_ERR_ALIGN;
+  const int64_t rows = ffnk_route_capacity(M) + BM;
+  CUtensorMap tmA, tmB[4];
+  int r = make_tensor_map_2d(&tmA, inter, h, rows, ldi, BK, BM);
+  if (r) return r;
+  bool mn1 = false, mn2 = false;
+  if ((r = weight_map(&tmB[0], WeightView{w2, w_stride_k, w_stride_n, h, d}, &mn1))) return r;
+  if ((r = weight_map(&tmB[2], WeightView{u2, w_stride_k, w_stride_n, h, d}, &mn2))) return r;
+  tmB[1] = tmB[0];
+  tmB[3] = tmB[2];
+  GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(y), ldy, static_cast<int>(d), static_cast<int>(h),
+               static_cast<int>(M), pick_group_m(h), status};
+  return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1,
+                                                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
+                               int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm, const int32_t* counts,
+                               void* da, int64_t ldda, void* db1, void* db2, int64_t M, int64_t N, int64_t K,
+                               int32_t* status, void* stream) {
+  if (!db1 || !db2) return FFNK_ERR_NULL;
+  if (bad_dim(N) || bad_dim(K) || M < 0 || M >= (1ll << 30)) return FFNK_ERR_SHAPE;
+  const bool k_major = (b_stride_k == 1 && b_stride_n >= K);   // storage [N, K]
+  const bool n_major = (b_stride_n == 1 && b_stride_k >= N);   // storage [K, N]
+  if (!k_major && !n_major) return FFNK_ERR_LAYOUT;
+  if ((reinterpret_cast<uintptr_t>(db1) & 15) || (reinterpret_cast<uintptr_t>(db2) & 15)) return FFNK_ERR_ALIGN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (M == 0) {
+    // no tokens: both weight gradients are zero (strided fill, row by row of the storage)
+    const int64_t rows = k_major ? N : K, cols = k_major ? K : N, ld = k_major ? b_stride_n : b_stride_k;
+    cudaError_t e = cudaMemset2DAsync(db1, ld * 2, 0, cols * 2, rows, s);
+    if (e == cudaSuccess) e = cudaMemset2DAsync(db2, ld * 2, 0, cols * 2, rows, s);
+    return cuda_status(e);
+  }
+  if (!g || !a || !b1 || !b2 || !perm || !counts || !da) return FFNK_ERR_NULL;
+  if ((ldg & 7) || (lda & 7) || (ldda & 7) || ldg < N || lda < K || ldda < K ||
+      (reinterpret_cast<uintptr_t>(da) & 15))
+    return FFNK_ERR_ALIGN;
+  const DeviceInfo& dev = device_info();
+  if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
+
+  // dx: the forward kernel on g with the weights seen as [N, K] (contraction over N)
+  {
+    CUtensorMap tmA, tmB[4];
+    int r = make_tensor_map_2d(&tmA, g, N, M, ldg, BK, 1);
+    if (r) return r;
+    bool mn1 = false, mn2 = false;
+    if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_n, b_stride_k, N, K}, &mn1))) return r;
+    if ((r = weight_map(&tmB[2], WeightView{b2, b_stride_n, b_stride_k, N, K}, &mn2))) return r;
+    tmB[1] = tmB[0];
+    tmB[3] = tmB[2];
+    GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(da), ldda, static_cast<int>(K), static_cast<int>(N),
+                 static_cast<int>(M), pick_group_m(N), status};
+    r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1, s);
+    if (r) return r;
+  }
+  // dW: output in the weight's storage order; P supplies the storage rows, Q the storage columns
+  {
+    const void* P = k_major ? g : a;
+    const void* Q = k_major ? a : g;
+    const int64_t ldp = k_major ? ldg : lda, ldq = k_major ? lda : ldg;
+    const int64_t p_dim = k_major ? N : K, q_dim = k_major ? K : N;
+    CUtensorMap tmP, tmQ;
+    int r = make_tensor_map_2d(&tmP, P, p_dim, M, ldp, 64, 1);
+    if (r) return r;
+    if ((r = make_tensor_map_2d(&tmQ, Q, q_dim, M, ldq, 64, 1))) return r;
+    WgradParams wp{perm, counts, static_cast<__nv_bfloat16*>(db1), static_cast<__nv_bfloat16*>(db2),
+                   k_major ? b_stride_n : b_stride_k, static_cast<int>(p_dim), static_cast<int>(q_dim),
+                   static_cast<int>(M), status};
+    int64_t grid = 2 * ((p_dim + BM - 1) / BM) * ((q_dim + BN - 1) / BN);
+    if (grid > dev.sm_count) grid = dev.sm_count;
+    cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (e != cudaSuccess) return cuda_status(e);
+    wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
+    return cuda_status(cudaGetLastError());
+  }
+}

@@ -1,0 +1,84 @@
+"""Host launchers of the routed MaskedFFN kernels.
+
+``_bf16_ffn_forward`` keeps the name, arguments and result of the reference launcher
+(``ffn_kernel/ffn.py:527-560``): the SwiGLU intermediate ``silu(x w1) * (x w3)`` (``u1``/``u3``
+for text rows) as an [M, h] tensor in token order.  ``_bf16_ffn_fused_forward`` is the whole
+``MaskedFFN.forward`` (``ffn_kernel/ops.py:28-32``): it keeps the intermediate in routed
+order, so the down projection reads it with plain tiled loads and scatters the result rows
+back to token order in its epilogue.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, lib
+from .linear import _activation, _check_dims, _mask_route, _weights
+from .route import Route, maybe_check, status_word, stream_ptr
+
+
+def _bf16_ffn_forward(x, w1, w3, u1, u3, mask, rt: Route | None = None):
+    """x [M,d]; w1,w3,u1,u3 [d,h]; mask [M] -> [M,h] bf16 in token order."""
+    x = _activation(x, "x")
+    M, d = x.shape
+    h = w1.shape[1] if isinstance(w1, torch.Tensor) and w1.dim() == 2 else -1
+    w1, w3, u1, u3 = _weights((w1, w3, u1, u3), ("w1", "w3", "u1", "u3"), d, h)
+    _check_dims(d=d, h=h)
+    dev = x.device
+    with torch.cuda.device(dev):
+        out = torch.empty((M, h), device=dev, dtype=torch.bfloat16)
+        if M == 0:
+            return out
+        rt = _mask_route(mask, M, dev, rt)
+        check("ffnk_ffn_gateup", lib().ffnk_ffn_gateup(
+            x.data_ptr(), x.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),
+            w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), out.data_ptr(), out.stride(0),
+            0, M, d, h, status_word(dev).data_ptr(), stream_ptr(dev)))
+    maybe_check(dev)
+    return out
+
+
+def decode_max_tokens() -> int:
+    return int(lib().ffnk_decode_max_tokens())
+
+
+def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = None,
+                            allow_decode: bool = True):
+    """The full forward: y[m] = (silu(x[m] W1) * (x[m] W3)) W2 with the modality's weights.
+
+    Small token counts take the weight-streaming decode kernels, everything else the two
+    routed GEMMs.  Argument order follows ``MaskedFFN.apply`` (``ffn_kernel/ops.py:30``)."""
+    x = _activation(x, "x")
+    M, d = x.shape
+    h = w1.shape[1] if isinstance(w1, torch.Tensor) and w1.dim() == 2 else -1
+    w1, w3, u1, u3 = _weights((w1, w3, u1, u3), ("w1", "w3", "u1", "u3"), d, h)
+    w2, u2 = _weights((w2, u2), ("w2", "u2"), h, d)
+    _check_dims(d=d, h=h)
+    dev = x.device
+    L = lib()
+    with torch.cuda.device(dev):
+        y = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
+        if M == 0:
+            return y
+        st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
+        if allow_decode and rt is None and M <= decode_max_tokens():
+            if mask.dim() != 1 or mask.shape[0] != M or mask.device != dev:
+                raise RuntimeError(f"mask must have shape [{M}] on {dev}")
+            m8 = mask.contiguous()
+            inter = torch.empty((M, h), device=dev, dtype=torch.float32)
+            check("ffnk_ffn_decode", L.ffnk_ffn_decode(
+                x.data_ptr(), x.stride(0), w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), u1.data_ptr(),
+                u2.data_ptr(), u3.data_ptr(), w1.stride(0), w1.stride(1), w2.stride(0), w2.stride(1),
+                m8.data_ptr(), inter.data_ptr(), y.data_ptr(), y.stride(0), M, d, h, st, sp))
+            maybe_check(dev)
+            return y
+        rt = _mask_route(mask, M, dev, rt)
+        inter = torch.empty((rt.cap + 128, h), device=dev, dtype=torch.bfloat16)
+        check("ffnk_ffn_gateup", L.ffnk_ffn_gateup(
+            x.data_ptr(), x.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),
+            w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), inter.stride(0),
+            1, M, d, h, st, sp))
+        check("ffnk_ffn_down", L.ffnk_ffn_down(
+            inter.data_ptr(), inter.stride(0), w2.data_ptr(), u2.data_ptr(), w2.stride(0), w2.stride(1),
+            rt.perm.data_ptr(), rt.counts.data_ptr(), y.data_ptr(), y.stride(0), M, d, h, st, sp))
+    maybe_check(dev)
+    return y

@@ -1,0 +1,125 @@
+"""Host launchers of the routed MaskedLinear kernels.
+
+Same names and argument meaning as the reference's launchers
+(``ffn_kernel/linear.py:418-452`` ``_bf16_linear_forward``,
+``ffn_kernel/linear.py:455-496`` ``_bf16_linear_backward``); the Triton kernels and the
+JSON tile table behind them are replaced by calls into libffnk.so (hand-written sm_100a
+CUDA).  Tile shapes are fixed per kernel in the library, not looked up from a config.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, lib
+from .route import Route, _require_cuda, maybe_check, route, status_word, stream_ptr
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+    return t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.stride(0) >= t.shape[1] and t.data_ptr() % 16 == 0
+
+
+def _activation(t: torch.Tensor, name: str) -> torch.Tensor:
+    """2-D bf16 CUDA activation with 16-byte aligned rows (copied only if it has to be,
+    as the reference does with ``.contiguous()``, ``ffn_kernel/linear.py:430``)."""
+    _require_cuda(t, name)
+    if t.dim() != 2:
+        raise RuntimeError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+    if t.dtype != torch.bfloat16:
+        raise RuntimeError(f"{name} must be torch.bfloat16, got {t.dtype}")
+    return t if _rows_ok(t) else t.contiguous()
+
+
+def _weight_ok(w: torch.Tensor) -> bool:
+    K, N = w.shape
+    if w.data_ptr() % 16:
+        return False
+    if w.stride(0) == 1 and w.stride(1) >= K and w.stride(1) % 8 == 0:
+        return True
+    return w.stride(1) == 1 and w.stride(0) >= N and w.stride(0) % 8 == 0
+
+
+def _weights(ws, names, K, N):
+    """Logical [K, N] bf16 weights, either the ``nn.Linear.weight.T`` view (stride_k == 1) or
+    contiguous (stride_n == 1).  All weights of one call must share one layout; anything
+    else is copied to contiguous [K, N]."""
+    for w, n in zip(ws, names):
+        _require_cuda(w, n)
+        if w.dim() != 2 or tuple(w.shape) != (K, N):
+            raise RuntimeError(f"{n} must have shape [{K}, {N}], got {tuple(w.shape)}")
+        if w.dtype != torch.bfloat16:
+            raise RuntimeError(f"{n} must be torch.bfloat16, got {w.dtype}")
+    strides = {tuple(w.stride()) for w in ws}
+    if len(strides) != 1 or not all(_weight_ok(w) for w in ws):
+        ws = [w.contiguous() for w in ws]
+    return list(ws)
+
+
+def _check_dims(**dims):
+    for n, v in dims.items():
+        if v < 8 or v % 8:
+            raise RuntimeError(f"{n} = {v} must be a positive multiple of 8 (16-byte rows of bf16)")
+
+
+def _mask_route(mask, M, device, rt: Route | None) -> Route:
+    if rt is not None:
+        if rt.M != M:
+            raise RuntimeError(f"route was built for M = {rt.M}, got M = {M}")
+        return rt
+    _require_cuda(mask, "mask")
+    if mask.dim() != 1 or mask.shape[0] != M:
+        raise RuntimeError(f"mask must have shape [{M}], got {tuple(mask.shape)}")
+    if mask.device != device:
+        raise RuntimeError("mask must be on the same device as the activations")
+    return route(mask)
+
+
+def _bf16_linear_forward(a, b1, b2, mask, rt: Route | None = None):
+    """c[m] = a[m] @ (b1 if mask[m] else b2).  a [M,K], b1/b2 [K,N], mask [M] -> [M,N] bf16."""
+    a = _activation(a, "a")
+    M, K = a.shape
+    N = b1.shape[1] if isinstance(b1, torch.Tensor) and b1.dim() == 2 else -1
+    b1, b2 = _weights((b1, b2), ("b1", "b2"), K, N)
+    _check_dims(K=K, N=N)
+    dev = a.device
+    with torch.cuda.device(dev):
+        c = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+        if M == 0:
+            return c
+        rt = _mask_route(mask, M, dev, rt)
+        check("ffnk_linear_fwd", lib().ffnk_linear_fwd(
+            a.data_ptr(), a.stride(0), b1.data_ptr(), b2.data_ptr(), b1.stride(0), b1.stride(1),
+            rt.perm.data_ptr(), rt.counts.data_ptr(), c.data_ptr(), c.stride(0), M, N, K,
+            status_word(dev).data_ptr(), stream_ptr(dev)))
+    maybe_check(dev)
+    return c
+
+
+def _bf16_linear_backward(gd, a, b1, b2, mask, rt: Route | None = None):
+    """Returns (da, db1, db2); db1/db2 carry the strides of b1/b2 (``empty_like``,
+    ``ffn_kernel/linear.py:475``)."""
+    a = _activation(a, "a")
+    M, K = a.shape
+    N = b1.shape[1] if isinstance(b1, torch.Tensor) and b1.dim() == 2 else -1
+    _require_cuda(gd, "grad")
+    if tuple(gd.shape) != (M, N):
+        raise RuntimeError(f"grad must have shape [{M}, {N}], got {tuple(gd.shape)}")
+    gd = _activation(gd, "grad")
+    b1, b2 = _weights((b1, b2), ("b1", "b2"), K, N)
+    _check_dims(K=K, N=N)
+    dev = a.device
+    with torch.cuda.device(dev):
+        da = torch.empty((M, K), device=dev, dtype=torch.bfloat16)
+        db1, db2 = torch.empty_like(b1), torch.empty_like(b2)
+        if tuple(db1.stride()) != tuple(b1.stride()) or tuple(db2.stride()) != tuple(b1.stride()):
+            db1 = torch.empty_strided(b1.shape, b1.stride(), device=dev, dtype=torch.bfloat16)
+            db2 = torch.empty_strided(b1.shape, b1.stride(), device=dev, dtype=torch.bfloat16)
+        if M == 0:
+            return da, db1.zero_(), db2.zero_()
+        rt = _mask_route(mask, M, dev, rt)
+        check("ffnk_linear_bwd", lib().ffnk_linear_bwd(
+            gd.data_ptr(), gd.stride(0), a.data_ptr(), a.stride(0), b1.data_ptr(), b2.data_ptr(),
+            b1.stride(0), b1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(),
+            da.data_ptr(), da.stride(0), db1.data_ptr(), db2.data_ptr(), M, N, K,
+            status_word(dev).data_ptr(), stream_ptr(dev)))
+    maybe_check(dev)
+    return da, db1, db2

@@ -1,0 +1,138 @@
+/*
+ * ffnk.h -- C ABI of the B200 (sm_100a) routed MaskedLinear / MaskedFFN kernels.
+ *
+ * Plain pointers and sizes only.  Every pointer is a DEVICE pointer on the current CUDA
+ * device unless stated otherwise; `stream` is a cudaStream_t passed as void*.  Nothing here
+ * allocates or synchronises unless its comment says so: the caller owns every buffer
+ * (outputs, routing lists, scratch) and orders work by stream.
+ *
+ * Return value: 0 on success; a negative FFNK_ERR_* for a rejected argument (nothing was
+ * launched); -(1000 + cudaError_t) for a CUDA runtime error reported at launch.  Device-side
+ * protocol errors (a bounded wait that expired) are written as small positive codes to the
+ * int32 status word the caller passes and read back with ffnk_read_status().
+ *
+ * Citations are file:line in the reference project (wenhaoli-xmu/ffn_kernel) whose host
+ * launchers these entry points replace.
+ *
+ * Conventions shared by all entry points
+ *   - Activations are bf16, row-major with an element row stride (`ld*`), 16-byte aligned rows.
+ *   - A weight is the logical [K, N] matrix the reference's operators receive (b1/b2, w*, u*).
+ *     It is described by its element strides (stride_k, stride_n); exactly one of them must
+ *     be 1.  stride_k == 1 is the `nn.Linear.weight.T` view (storage [N, K]); stride_n == 1
+ *     is a contiguous [K, N] matrix.  No transposed copy is ever made.
+ *   - mask: one byte per token, non-zero = first weight set ("visual"), zero = second ("text")
+ *     (ffn_kernel/linear.py:137-140).
+ *   - Routing lists (`perm`, `counts`) are produced by ffnk_route() on the same stream.
+ */
+#ifndef FFNK_H_
+#define FFNK_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FFNK_ERR_NULL (-1)      /* a required pointer is null */
+#define FFNK_ERR_SHAPE (-2)     /* a size is negative, too large or not a multiple of 8 */
+#define FFNK_ERR_ALIGN (-3)     /* a base pointer or row stride is not 16-byte aligned */
+#define FFNK_ERR_LAYOUT (-4)    /* a weight has neither stride_k == 1 nor stride_n == 1 */
+#define FFNK_ERR_DRIVER (-5)    /* the CUDA driver entry point for tensor maps is unavailable */
+#define FFNK_ERR_TENSORMAP (-6) /* the driver rejected a tensor map */
+#define FFNK_ERR_DEVICE (-7)    /* the current device is not compute capability 10.x */
+
+/* Library version (major * 100 + minor). */
+int ffnk_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Routing.  No counterpart as a function in the reference: it replaces the per-tile
+ * uniformity test of every reference kernel (ffn_kernel/linear.py:132,137;
+ * ffn_kernel/ffn.py:72,79) by explicit per-modality row lists.
+ *
+ *   cap  = ffnk_route_capacity(M)           (M rounded up to a multiple of 128)
+ *   perm   int32[2 * cap], 16-byte aligned: perm[0..Mv) ascending visual rows,
+ *                                           perm[cap..cap+Mt) ascending text rows
+ *   counts int32[4] = { Mv, Mt, cap, M }    (stay on the device; no host sync)
+ *   workspace: ffnk_route_workspace_bytes(M) bytes, cleared by the call itself
+ * ------------------------------------------------------------------------------------- */
+int64_t ffnk_route_capacity(int64_t M);
+int64_t ffnk_route_workspace_bytes(int64_t M);
+int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* counts, void* workspace, int32_t* status,
+               void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * MaskedLinear forward.  Replaces _bf16_linear_forward (ffn_kernel/linear.py:418-452) and
+ * the kernel it launches (_masked_matmul_infer, ffn_kernel/linear.py:76-159):
+ *     c[m, :] = a[m, :] @ (mask[m] ? b1 : b2)        a [M,K], b* [K,N], c [M,N] bf16
+ * bf16 operands, fp32 accumulation, bf16 output.  Every row of c is written exactly once.
+ * ------------------------------------------------------------------------------------- */
+int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const void* b2, int64_t b_stride_k,
+                    int64_t b_stride_n, const int32_t* perm, const int32_t* counts, void* c, int64_t ldc, int64_t M,
+                    int64_t N, int64_t K, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * MaskedLinear backward.  Replaces _bf16_linear_backward (ffn_kernel/linear.py:455-496) and
+ * _fused_bwd_kernel / _masked_matmul_bwd_da / _masked_matmul_bwd_db
+ * (ffn_kernel/linear.py:15-72, 242-326, 329-415):
+ *     da[m, :] = g[m, :] @ (mask[m] ? b1 : b2)^T
+ *     db1 = a[mask]^T @ g[mask],   db2 = a[~mask]^T @ g[~mask]
+ * db1/db2 are written with the same strides as b1/b2 (the reference allocates them with
+ * empty_like, ffn_kernel/linear.py:475).
+ * ------------------------------------------------------------------------------------- */
+int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
+                    int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm, const int32_t* counts, void* da,
+                    int64_t ldda, void* db1, void* db2, int64_t M, int64_t N, int64_t K, int32_t* status,
+                    void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * MaskedFFN gate/up projection with the SwiGLU epilogue.  Replaces _bf16_ffn_forward
+ * (ffn_kernel/ffn.py:527-560) and _masked_ffn_infer (ffn_kernel/ffn.py:15-113):
+ *     t1 = x @ (mask ? w1 : u1),  t3 = x @ (mask ? w3 : u3),  out = silu(t1) * t3
+ * x [M,d]; w1,w3,u1,u3 [d,h] sharing one pair of strides; out bf16.
+ *   routed_out == 0: out is [M, h] in token order (what the reference function returns).
+ *   routed_out != 0: out is the routed intermediate [(cap + 128), h]: visual rows first,
+ *                    text rows from row 128 * ceil(Mv / 128); rows in between are not written.
+ * ------------------------------------------------------------------------------------- */
+int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1, const void* u3,
+                    int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* out,
+                    int64_t ldo, int routed_out, int64_t M, int64_t d, int64_t h, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * MaskedFFN down projection from the routed intermediate, rows scattered back to token order
+ * in the epilogue.  Together with ffnk_ffn_gateup(routed_out = 1) this replaces
+ * MaskedFFN.forward (ffn_kernel/ops.py:28-32), whose second step is _bf16_linear_forward on
+ * the intermediate:
+ *     y[token, :] = inter[routed row of token, :] @ (mask[token] ? w2 : u2)
+ * inter [(cap + 128), h] as written by ffnk_ffn_gateup; w2,u2 [h,d]; y [M,d] bf16.
+ * ------------------------------------------------------------------------------------- */
+int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
+                  int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy, int64_t M,
+                  int64_t d, int64_t h, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Small-M (decode) MaskedFFN forward: streams each present modality's weights once with
+ * 128-bit loads; same contract as MaskedFFN.forward (ffn_kernel/ops.py:28-32).
+ * inter: scratch fp32 [M, h].  Supported for M <= ffnk_decode_max_tokens().
+ * ------------------------------------------------------------------------------------- */
+int ffnk_decode_max_tokens(void);
+int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
+                    const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n, int64_t w2_stride_k,
+                    int64_t w2_stride_n, const void* mask, void* inter, void* y, int64_t ldy, int64_t M, int64_t d,
+                    int64_t h, int32_t* status, void* stream);
+
+/* Synchronises `stream`, copies the status word to the host and returns it (0 = ok, >0 one of
+ * the device status codes, <0 an error as above).  If `clear` is non-zero the word is reset to 0. */
+int ffnk_read_status(int32_t* status, int clear, void* stream);
+
+/* Exercises the bounded-wait path on purpose: one CTA waits on a barrier nobody arrives on,
+ * with a budget of `budget_us` microseconds, then records its status and exits normally.
+ * Used by the tests to show that an expired wait surfaces as a status code. */
+int ffnk_selftest_bounded_wait(int32_t* status, int64_t budget_us, void* stream);
+
+/* Human-readable name of a return code or device status code (static storage). */
+const char* ffnk_status_string(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FFNK_H_ */
