@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of the routed MaskedFFN forward (d = 4096, h = 11008, M = 16384 tokens) on B200.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference            # the reference's PyTorch module on the host cores
+
+A step is one ``MaskedFFN.apply`` over one batch of synthetic tokens: routing scan, gate/up GEMM
+with the SwiGLU epilogue, down projection with the scatter epilogue.  ``value`` is routed useful
+TFLOP/s (6*M*d*h per step: each token times its own modality's weights only) with inputs resident
+in HBM; ``e2e`` is the same metric with the step's activations and mask starting in pinned host
+memory and the result ending there.  Rank 0 prints one JSON line.
+
+N > 1 runs the tensor-parallel mode by default (weights sharded over h, partial outputs summed by
+NCCL all-reduce, total work fixed: strong scaling); ``--mode dp`` runs token-sharded data
+parallel (every rank its own batch, no communication: weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "c4_ffn_d4096_h11008_m16384": dict(M=16384, d=4096, h=11008),
+    "c2_ffn_d1024_h2048_m32768": dict(M=32768, d=1024, h=2048),
+}
+METRIC = "routed_bf16_tflops_maskedffn_fwd"
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return dict(tflops=float(p["bf16_tflops"]), hbm=float(p["hbm_gbs"]), source="measured")
+    except Exception:
+        return dict(tflops=1590.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        busy = [v for v in sm if v > 0.5 * max(sm)] or sm
+        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's PyTorch module arithmetic on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_rate(case, sample_rows: int, steps: int, warmup: int):
+    """bf16 CPU evaluation of the reference module (both branches dense, then mask-select) on the
+    first `sample_rows` tokens of the workload.  Returns (useful TFLOP/s, seconds per pass)."""
+    from oracle import masked_ref as O
+    args = case.apply_args()
+    x, mask = args[0][:sample_rows], args[7][:sample_rows]
+    d, h = args[1].shape
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.masked_ffn(x, *args[1:7], mask, dtype=torch.bfloat16)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return 6.0 * sample_rows * d * h / t / 1e12, t
+
+
+def run_reference(args):
+    from ffn_kernel_b200.synth import ffn_case
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    wl = WORKLOADS[args.workload]
+    case = ffn_case(wl["M"], wl["d"], wl["h"], seed=0)
+    rows = min(args.cpu_sample_rows, wl["M"])
+    tf, sec = cpu_reference_rate(case, rows, max(1, args.steps), max(0, args.warmup))
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, **wl, "mask": "image spans of 576 tokens, ~50% visual"},
+        "tokens_per_s": rows / sec,
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"first {rows} of {wl['M']} tokens per step, full weights; torch CPU bf16, "
+                                   "both branches dense then mask-selected as the reference module does"},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+    from ffn_kernel_b200 import MaskedFFN, check_status, tp
+    from ffn_kernel_b200 import ffn as ffn_mod
+    from ffn_kernel_b200.synth import ffn_case
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    wl = WORKLOADS[args.workload]
+    M, d, h = wl["M"], wl["d"], wl["h"]
+    mode = "single" if world == 1 else args.mode
+    seed = rank if mode == "dp" else 0          # dp: every rank has its own batch
+    case_cpu = ffn_case(M, d, h, seed=seed)
+    case = case_cpu.to(dev)
+    full_args = case.apply_args()
+    if mode == "tp":
+        weights = tp.shard_ffn_weights(*full_args[1:7], rank, world)
+    else:
+        weights = full_args[1:7]
+    x, mask = full_args[0], full_args[7]
+    h_local = weights[0].shape[1]
+
+    def step(xi=x, mi=mask):
+        if mode == "tp":
+            return tp.masked_ffn_tp(xi, *weights, mi, chunks=args.chunks)
+        return MaskedFFN.apply(xi, *weights, mi)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- kernel-resident timing --------------------------------------------------------------
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    check_status()
+
+    phase_events = []
+
+    def hook(name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        phase_events.append((name, ev))
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    ffn_mod.PHASE_HOOK = hook
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    ffn_mod.PHASE_HOOK = None
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    check_status()
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+
+    # gate/up launch durations from the events recorded on the launching stream
+    names = [n for n, _ in phase_events]
+    gateup_ms, down_ms, route_ms = [], [], []
+    for i in range(len(phase_events) - 1):
+        n, ev = phase_events[i]
+        dt = ev.elapsed_time(phase_events[i + 1][1])
+        if n == "gateup" and names[i + 1] == "down":
+            gateup_ms.append(dt)
+        elif n == "down" and names[i + 1] == "end":
+            down_ms.append(dt)
+        elif n == "route" and names[i + 1] == "gateup":
+            route_ms.append(dt)
+    n_ffn_calls = len(gateup_ms)
+    rows_per_call = M / max(1, (args.chunks if mode == "tp" else 1))
+
+    total_flops_per_step = 6.0 * M * d * h * (world if mode == "dp" else 1)
+    value = total_flops_per_step / (ms_per_step * 1e-3) / 1e12
+    tokens_per_s = M * (world if mode == "dp" else 1) / (ms_per_step * 1e-3)
+
+    peaks = measured_peaks()
+    roofline = None
+    if gateup_ms:
+        g_ms = statistics.mean(gateup_ms)
+        achieved = 4.0 * rows_per_call * d * h_local / (g_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "routed_gemm_kernel<gather, swiglu, routed> (gate/up)",
+                    "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
+                    "peak_source": f"{peaks['source']} burst bf16 (MEASURED_PEAKS.json)",
+                    "launch_ms": g_ms, "down_launch_ms": statistics.mean(down_ms) if down_ms else None,
+                    "route_launch_ms": statistics.mean(route_ms) if route_ms else None,
+                    "traffic": args.traffic_bytes}
+
+    # ---- end to end: activations and mask start in pinned host memory, result ends there -------
+    e2e = None
+    if not args.skip_e2e:
+        xh = case_cpu.x.pin_memory()
+        mh = case_cpu.mask.pin_memory()
+        out_rows = tp.row_shard(M, rank, world) if mode == "tp" else slice(0, M)
+        n_out = out_rows.stop - out_rows.start
+        yh = [torch.empty((n_out, d), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        xd = [torch.empty_like(x) for _ in range(2)]
+        md = [torch.empty_like(mask) for _ in range(2)]
+        s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_done = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
+
+        def e2e_steps(n):
+            for i in range(n):
+                b = i & 1
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(ev_done[b])           # the step that last read this input buffer
+                    xd[b].copy_(xh, non_blocking=True)
+                    md[b].copy_(mh, non_blocking=True)
+                    ev_in[b].record(s_in)
+                s_main.wait_event(ev_in[b])
+                y = step(xd[b], md[b])
+                ev_done[b].record(s_main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[b])
+                    s_out.wait_event(ev_out[b])           # previous read-back into this host buffer
+                    yh[b].copy_(y[out_rows], non_blocking=True)
+                    ev_out[b].record(s_out)
+                y.record_stream(s_out)
+
+        e2e_steps(max(2, min(args.warmup, 4)))
+        barrier()
+        t0 = time.perf_counter()
+        e2e_steps(args.steps)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e2e_s = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([e2e_s], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        check_status()
+        e2e = {"value": total_flops_per_step * args.steps / e2e_s / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int((xh.numel() * 2 + mh.numel()) * world),
+               "d2h_bytes_per_step": int(M * d * 2 * (world if mode == "dp" else 1)),
+               "ms_per_step": e2e_s / args.steps * 1e3,
+               "tokens_per_s": M * (world if mode == "dp" else 1) * args.steps / e2e_s,
+               "pipeline": "H2D of step i+1, compute of step i and D2H of step i-1 overlap on three streams"}
+
+    # ---- CPU baseline (rank 0, single GPU only) -------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        rows = min(args.cpu_sample_rows, M)
+        tf, sec = cpu_reference_rate(case_cpu, rows, steps=3, warmup=1)
+        cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"first {rows} of {M} tokens, full weights, median of 3 passes ({sec:.2f} s each); torch CPU "
+                         "bf16, both branches dense then mask-selected as the reference module does"}
+
+    if rank == 0:
+        kernels_per_call = 3      # routing scan, gate/up GEMM, down GEMM
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak" if mode == "dp" else "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "M": M, "d": d, "h": h, "parallelism": f"{mode}{world}",
+                       "tp_chunks": args.chunks if mode == "tp" else None,
+                       "mask": f"image spans of 576 tokens, {float(case_cpu.mask.float().mean()):.3f} visual",
+                       "l2": "inputs larger than L2 (activations 128 MiB + weights 516 MiB per step)"
+                       if args.workload.startswith("c4") else "inputs larger than L2"},
+            "tokens_per_s": tokens_per_s,
+            "frac_of_measured_bf16_peak": value / peaks["tflops"] / world,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": kernels_per_call * max(1, n_ffn_calls),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c4_ffn_d4096_h11008_m16384")
+    ap.add_argument("--mode", choices=["tp", "dp"], default="tp", help="multi-GPU mode (N > 1)")
+    ap.add_argument("--chunks", type=int, default=4, help="token chunks per step in tp mode (overlap)")
+    ap.add_argument("--cpu-sample-rows", type=int, default=1024)
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--traffic-bytes", type=float, default=None,
+                    help="DRAM bytes per gate/up launch from an ncu capture (profiles/), if known")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -61,9 +61,7 @@ def lib() -> ctypes.CDLL:
                 "Run `python -m ffn_kernel_b200.build` (needs nvcc); there is no CPU or Triton fallback.")
         handle = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
-            fn = getattr(handle, name, None)
-            if fn is None:   # TEMP while kernels are being brought up
-                continue
+            fn = getattr(handle, name)      # AttributeError if the library lacks a declared symbol
             fn.restype, fn.argtypes = res, args
         _lib = handle
     return _lib

@@ -1,5 +1,7 @@
 // Host utilities of libffnk: device query, tensor-map construction, status word access,
 // and the bounded-wait self test.
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "ffnk_internal.h"
@@ -43,6 +45,18 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint6
                        uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return FFNK_ERR_DRIVER;
+  // The encoder is a driver-API call and needs the device's primary context current on the
+  // calling thread; a thread that has only made query calls so far (autograd's backward
+  // thread, for one) may not have it bound yet.  cudaFree(0) binds it.
+  {
+    thread_local int bound_device = -1;
+    int dev = -1;
+    cudaGetDevice(&dev);
+    if (dev != bound_device) {
+      cudaFree(0);
+      bound_device = dev;
+    }
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((row_stride * 2) & 15)) return FFNK_ERR_ALIGN;
   if (inner == 0 || outer == 0) return FFNK_ERR_SHAPE;
   const cuuint64_t dims[2] = {inner, outer};
@@ -52,6 +66,10 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint6
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && getenv("FFNK_VERBOSE"))
+    fprintf(stderr, "ffnk: cuTensorMapEncodeTiled failed (CUresult %d): base %p dims {%llu, %llu} row stride %llu B box {%u, %u}\n",
+            static_cast<int>(r), base, static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+            static_cast<unsigned long long>(row_stride * 2), box_inner, box_outer);
   return r == CUDA_SUCCESS ? 0 : FFNK_ERR_TENSORMAP;
 }
 

@@ -97,7 +97,8 @@ __device__ __forceinline__ float silu_mul(float t1, float t3) {
 
 template <int A_MODE, int EPI, int OUT_MODE, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBv0,
+routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA32,
+                   const __grid_constant__ CUtensorMap tmA128, const __grid_constant__ CUtensorMap tmBv0,
                    const __grid_constant__ CUtensorMap tmBv1, const __grid_constant__ CUtensorMap tmBt0,
                    const __grid_constant__ CUtensorMap tmBt1, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -124,6 +125,8 @@ routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmA32);
+    tma_prefetch_desc(&tmA128);
     tma_prefetch_desc(&tmBv0);
     tma_prefetch_desc(&tmBv1);
     tma_prefetch_desc(&tmBt0);
@@ -155,6 +158,9 @@ routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_v, m_tiles, n_tiles, p.group_m, Mv, Mt, cap);
       int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
+      // How this lane's rows are fetched: 0 = gather4 of its four rows, 1 = its 32-row quarter of
+      // the tile is one run of consecutive tokens (one tiled box per quarter), 2 = the whole tile is.
+      int run_mode = 0;
       if constexpr (A_MODE == A_GATHER) {
         const int lr = 4 * lane;  // first of this lane's four rows
         if (lr < tc.rows) {
@@ -164,6 +170,14 @@ routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (lr + 2 < tc.rows) r2 = v.z;
           if (lr + 3 < tc.rows) r3 = v.w;
         }
+        const bool lane_run = (lr + 3 < tc.rows) && r1 == r0 + 1 && r2 == r0 + 2 && r3 == r0 + 3;
+        const int qbase = __shfl_sync(0xFFFFFFFFu, r0, lane & ~7);
+        const int tbase = __shfl_sync(0xFFFFFFFFu, r0, 0);
+        const uint32_t q_ball = __ballot_sync(0xFFFFFFFFu, lane_run && r0 == qbase + 4 * (lane & 7));
+        const uint32_t t_ball = __ballot_sync(0xFFFFFFFFu, lane_run && r0 == tbase + lr);
+        const uint32_t q_bits = 0xFFu << (lane & ~7);
+        if (t_ball == 0xFFFFFFFFu) run_mode = 2;
+        else if ((q_ball & q_bits) == q_bits) run_mode = 1;
       }
       const CUtensorMap* mB0 = tc.text ? &tmBt0 : &tmBv0;
       const CUtensorMap* mB1 = tc.text ? &tmBt1 : &tmBv1;
@@ -182,7 +196,13 @@ routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         __syncwarp();
         const int kx = ks * BK;
         if constexpr (A_MODE == A_GATHER) {
-          tma_gather4(sa + lane * 512, &tmA, &full[stage], kx, r0, r1, r2, r3);
+          if (run_mode == 2) {
+            if (lane == 0) tma_load_2d(sa, &tmA128, &full[stage], kx, r0);
+          } else if (run_mode == 1) {
+            if ((lane & 7) == 0) tma_load_2d(sa + lane * 512, &tmA32, &full[stage], kx, r0);
+          } else {
+            tma_gather4(sa + lane * 512, &tmA, &full[stage], kx, r0, r1, r2, r3);
+          }
         } else {
           if (lane == 0) tma_load_2d(sa, &tmA, &full[stage], kx, tc.mt * BM);
         }
@@ -392,7 +412,9 @@ __device__ __forceinline__ WgradTile decode_wgrad_tile(int t, int p_tiles, int q
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const WgradParams p) {
+wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+             const __grid_constant__ CUtensorMap tmP32, const __grid_constant__ CUtensorMap tmQ32,
+             const WgradParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -418,6 +440,8 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CU
     fence_mbar_init();
     tma_prefetch_desc(&tmP);
     tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmP32);
+    tma_prefetch_desc(&tmQ32);
   }
   if (warp == 1) {
     tmem_alloc<1>(tmem_slot, TMEM_COLS);
@@ -446,16 +470,26 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CU
       if (wt.cnt == 0) continue;
       const int k_steps = (wt.cnt + BK - 1) / BK;
       const int* list = p.perm + wt.list_off;
+      const int4 pad4 = make_int4(p.pad_row, p.pad_row, p.pad_row, p.pad_row);
+      int4 nxt = (4 * gi < wt.cnt) ? *reinterpret_cast<const int4*>(list + 4 * gi) : pad4;
       for (int ks = 0; ks < k_steps; ++ks) {
         const int lr = ks * BK + 4 * gi;
+        const int4 v = nxt;
+        // the next k-step's rows are requested now so that the load is hidden behind this step
+        if (ks + 1 < k_steps) nxt = (lr + BK < wt.cnt) ? *reinterpret_cast<const int4*>(list + lr + BK) : pad4;
         int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
         if (lr < wt.cnt) {
-          const int4 v = *reinterpret_cast<const int4*>(list + lr);
           r0 = v.x;
           if (lr + 1 < wt.cnt) r1 = v.y;
           if (lr + 2 < wt.cnt) r2 = v.z;
           if (lr + 3 < wt.cnt) r3 = v.w;
         }
+        // 32 list rows that are consecutive tokens are fetched as one tiled box per column block
+        const bool lane_run = (lr + 3 < wt.cnt) && r1 == r0 + 1 && r2 == r0 + 2 && r3 == r0 + 3;
+        const int hbase = __shfl_sync(0xFFFFFFFFu, r0, lane & ~7);
+        const uint32_t ball = __ballot_sync(0xFFFFFFFFu, lane_run && r0 == hbase + 4 * (lane & 7));
+        const uint32_t bits = 0xFFu << (lane & ~7);
+        const bool run = (ball & bits) == bits;
         int w = 1;
         if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
         w = __shfl_sync(0xFFFFFFFFu, w, 0);
@@ -469,10 +503,21 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CU
         if (lane == 0) mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
         __syncwarp();
         // P: two 64-column blocks; Q: four.  Block b lives at b * 8 KiB, list row j at j * 128 B.
-        tma_gather4(sp + half * 8192 + gi * 512, &tmP, &full[stage], wt.pt * BM + half * 64, r0, r1, r2, r3);
-        tma_gather4(sq + half * 8192 + gi * 512, &tmQ, &full[stage], wt.qt * BN + half * 64, r0, r1, r2, r3);
-        tma_gather4(sq + (2 + half) * 8192 + gi * 512, &tmQ, &full[stage], wt.qt * BN + (2 + half) * 64, r0, r1, r2,
-                    r3);
+        uint8_t* dp = sp + half * 8192 + gi * 512;
+        uint8_t* dq0 = sq + half * 8192 + gi * 512;
+        uint8_t* dq1 = sq + (2 + half) * 8192 + gi * 512;
+        const int cp = wt.pt * BM + half * 64, cq0 = wt.qt * BN + half * 64, cq1 = wt.qt * BN + (2 + half) * 64;
+        if (run) {
+          if ((lane & 7) == 0) {
+            tma_load_2d(dp, &tmP32, &full[stage], cp, r0);
+            tma_load_2d(dq0, &tmQ32, &full[stage], cq0, r0);
+            tma_load_2d(dq1, &tmQ32, &full[stage], cq1, r0);
+          }
+        } else {
+          tma_gather4(dp, &tmP, &full[stage], cp, r0, r1, r2, r3);
+          tma_gather4(dq0, &tmQ, &full[stage], cq0, r0, r1, r2, r3);
+          tma_gather4(dq1, &tmQ, &full[stage], cq1, r0, r1, r2, r3);
+        }
         ++issued;
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
@@ -617,6 +662,15 @@ static int weight_map(CUtensorMap* m, const WeightView& w, bool* mn_major) {
   return FFNK_ERR_LAYOUT;
 }
 
+// The three views of a row-gathered activation matrix [rows, cols]: single rows for gather4,
+// and 32- and 128-row boxes for the parts of a tile that are runs of consecutive tokens.
+static int gather_maps(CUtensorMap (&m)[3], const void* base, int64_t cols, int64_t rows, int64_t ld) {
+  int r = make_tensor_map_2d(&m[0], base, cols, rows, ld, BK, 1);
+  if (r) return r;
+  if ((r = make_tensor_map_2d(&m[1], base, cols, rows, ld, BK, 32))) return r;
+  return make_tensor_map_2d(&m[2], base, cols, rows, ld, BK, BM);
+}
+
 static int pick_group_m(int64_t k_len) {
   // keep one super-tile of A rows (group_m x 128 rows x K) near 32 MiB so that it stays in L2
   // while the weights stream past it
@@ -627,7 +681,7 @@ static int pick_group_m(int64_t k_len) {
 }
 
 template <int A_MODE, int EPI, int OUT_MODE>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap (&tmB)[4], bool b_mn, const GemmParams& p,
+static int launch_gemm(const CUtensorMap (&tmA)[3], const CUtensorMap (&tmB)[4], bool b_mn, const GemmParams& p,
                        int64_t m_tiles_max, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
@@ -639,7 +693,8 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap (&tmB)[4], bool
   auto go = [&](auto kernel) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return cuda_status(e);
-    kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
+    kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, stream>>>(tmA[0], tmA[1], tmA[2], tmB[0], tmB[1],
+                                                                             tmB[2], tmB[3], p);
     return cuda_status(cudaGetLastError());
   };
   return b_mn ? go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, true>)
@@ -659,8 +714,8 @@ extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const
   if (!a || !b1 || !b2 || !perm || !counts || !c) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(N) || bad_dim(K)) return FFNK_ERR_SHAPE;
   if ((lda & 7) || (ldc & 7) || lda < K || ldc < N || (reinterpret_cast<uintptr_t>(c) & 15)) return FFNK_ERR_ALIGN;
-  CUtensorMap tmA, tmB[4];
-  int r = make_tensor_map_2d(&tmA, a, K, M, lda, BK, 1);
+  CUtensorMap tmA[3], tmB[4];
+  int r = gather_maps(tmA, a, K, M, lda);
   if (r) return r;
   bool mn1 = false, mn2 = false;
   if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_k, b_stride_n, K, N}, &mn1))) return r;
@@ -681,8 +736,8 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
   if (!x || !w1 || !w3 || !u1 || !u3 || !perm || !counts || !out) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
   if ((ldx & 7) || (ldo & 7) || ldx < d || ldo < h || (reinterpret_cast<uintptr_t>(out) & 15)) return FFNK_ERR_ALIGN;
-  CUtensorMap tmA, tmB[4];
-  int r = make_tensor_map_2d(&tmA, x, d, M, ldx, BK, 1);
+  CUtensorMap tmA[3], tmB[4];
+  int r = gather_maps(tmA, x, d, M, ldx);
   if (r) return r;
   bool mn = false, mn_i = false;
   const void* ws[4] = {w1, w3, u1, u3};
@@ -706,9 +761,10 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
   if ((ldi & 7) || (ldy & 7) || ldi < h || ldy < d || (reinterpret_cast<uintptr_t>(y) & 15)) return FFNK_ERR_ALIGN;
   const int64_t rows = ffnk_route_capacity(M) + BM;
-  CUtensorMap tmA, tmB[4];
-  int r = make_tensor_map_2d(&tmA, inter, h, rows, ldi, BK, BM);
+  CUtensorMap tmA[3], tmB[4];
+  int r = make_tensor_map_2d(&tmA[0], inter, h, rows, ldi, BK, BM);
   if (r) return r;
+  tmA[1] = tmA[2] = tmA[0];
   bool mn1 = false, mn2 = false;
   if ((r = weight_map(&tmB[0], WeightView{w2, w_stride_k, w_stride_n, h, d}, &mn1))) return r;
   if ((r = weight_map(&tmB[2], WeightView{u2, w_stride_k, w_stride_n, h, d}, &mn2))) return r;
@@ -747,8 +803,8 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
 
   // dx: the forward kernel on g with the weights seen as [N, K] (contraction over N)
   {
-    CUtensorMap tmA, tmB[4];
-    int r = make_tensor_map_2d(&tmA, g, N, M, ldg, BK, 1);
+    CUtensorMap tmA[3], tmB[4];
+    int r = gather_maps(tmA, g, N, M, ldg);
     if (r) return r;
     bool mn1 = false, mn2 = false;
     if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_n, b_stride_k, N, K}, &mn1))) return r;
@@ -766,10 +822,12 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     const void* Q = k_major ? a : g;
     const int64_t ldp = k_major ? ldg : lda, ldq = k_major ? lda : ldg;
     const int64_t p_dim = k_major ? N : K, q_dim = k_major ? K : N;
-    CUtensorMap tmP, tmQ;
+    CUtensorMap tmP, tmQ, tmP32, tmQ32;
     int r = make_tensor_map_2d(&tmP, P, p_dim, M, ldp, 64, 1);
     if (r) return r;
     if ((r = make_tensor_map_2d(&tmQ, Q, q_dim, M, ldq, 64, 1))) return r;
+    if ((r = make_tensor_map_2d(&tmP32, P, p_dim, M, ldp, 64, 32))) return r;
+    if ((r = make_tensor_map_2d(&tmQ32, Q, q_dim, M, ldq, 64, 32))) return r;
     WgradParams wp{perm, counts, static_cast<__nv_bfloat16*>(db1), static_cast<__nv_bfloat16*>(db2),
                    k_major ? b_stride_n : b_stride_k, static_cast<int>(p_dim), static_cast<int>(q_dim),
                    static_cast<int>(M), status};
@@ -777,7 +835,7 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     if (grid > dev.sm_count) grid = dev.sm_count;
     cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return cuda_status(e);
-    wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
+    wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, tmP32, tmQ32, wp);
     return cuda_status(cudaGetLastError());
   }
 }

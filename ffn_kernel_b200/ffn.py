@@ -37,6 +37,17 @@ def _bf16_ffn_forward(x, w1, w3, u1, u3, mask, rt: Route | None = None):
     return out
 
 
+# Optional observer called with a phase name ("route", "gateup", "down", "end") at the phase
+# boundaries of the fused forward, on the launching thread; the benchmark uses it to record
+# CUDA events on the launching stream.  None in normal use.
+PHASE_HOOK = None
+
+
+def _phase(name: str) -> None:
+    if PHASE_HOOK is not None:
+        PHASE_HOOK(name)
+
+
 def decode_max_tokens() -> int:
     return int(lib().ffnk_decode_max_tokens())
 
@@ -71,14 +82,18 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
                 m8.data_ptr(), inter.data_ptr(), y.data_ptr(), y.stride(0), M, d, h, st, sp))
             maybe_check(dev)
             return y
+        _phase("route")
         rt = _mask_route(mask, M, dev, rt)
         inter = torch.empty((rt.cap + 128, h), device=dev, dtype=torch.bfloat16)
+        _phase("gateup")
         check("ffnk_ffn_gateup", L.ffnk_ffn_gateup(
             x.data_ptr(), x.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),
             w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), inter.stride(0),
             1, M, d, h, st, sp))
+        _phase("down")
         check("ffnk_ffn_down", L.ffnk_ffn_down(
             inter.data_ptr(), inter.stride(0), w2.data_ptr(), u2.data_ptr(), w2.stride(0), w2.stride(1),
             rt.perm.data_ptr(), rt.counts.data_ptr(), y.data_ptr(), y.stride(0), M, d, h, st, sp))
+        _phase("end")
     maybe_check(dev)
     return y

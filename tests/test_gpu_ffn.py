@@ -1,0 +1,131 @@
+"""MaskedFFN forward on the GPU against the fp32 CPU oracle and the golden vectors of the
+reference's own module; called the way the reference's wrapper calls it (test_ffn.py:61-72)."""
+import pytest
+import torch
+
+from conftest import FFN_GOLDEN, TOL, load_golden
+from ffn_kernel_b200 import MaskedFFN, check_status
+from ffn_kernel_b200.ffn import _bf16_ffn_forward, _bf16_ffn_fused_forward, decode_max_tokens
+from ffn_kernel_b200.synth import edge_mask, ffn_case
+from oracle import masked_ref as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", FFN_GOLDEN)
+def test_forward_golden(dev, name):
+    z = load_golden(name)
+    B = z["x"].shape[0]
+    g = {k: v.to(dev) for k, v in z.items() if k in ("x", "mask", "w1", "w2", "w3", "u1", "u2", "u3")}
+    y = MaskedFFN.apply(g["x"].flatten(0, 1), g["w1"].T, g["w2"].T, g["w3"].T, g["u1"].T, g["u2"].T, g["u3"].T,
+                        g["mask"].flatten(0, 1)).unflatten(0, (B, -1))
+    check_status()
+    assert y.dtype == torch.bfloat16
+    assert O.max_rel_err(y, z["y_f32"]) < TOL
+
+
+@pytest.mark.parametrize("M,d,h", [(9, 64, 160), (127, 128, 256), (300, 128, 328), (1000, 1024, 2816),
+                                   (4099, 1024, 2816), (4096, 1024, 2048)])
+@pytest.mark.parametrize("kind", ["bernoulli", "span"])
+def test_forward_parity(dev, M, d, h, kind):
+    c = ffn_case(M, d, h, seed=M, mask=edge_mask(M, kind, seed=h))
+    ref = O.masked_ffn(*c.apply_args())
+    y = MaskedFFN.apply(*c.to(dev).apply_args())
+    check_status()
+    assert y.shape == (M, d) and y.is_contiguous()
+    assert O.max_rel_err(y, ref) < TOL
+
+
+@pytest.mark.parametrize("M", [1, 8, 64, 127, 1000, 4099])
+@pytest.mark.parametrize("kind", ["all_visual", "all_text", "alternating", "bernoulli"])
+def test_edge_and_decode_sweep(dev, M, kind):
+    # d = 1024, h = 2816 with every mask of the edge sweep, token counts around the tile size
+    c = ffn_case(M, 1024, 2816, seed=M, mask=edge_mask(M, kind, seed=1))
+    ref = O.masked_ffn(*c.apply_args())
+    y = MaskedFFN.apply(*c.to(dev).apply_args())
+    check_status()
+    assert O.max_rel_err(y, ref) < TOL
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_decode_and_gemm_paths_agree(dev, M):
+    assert M <= decode_max_tokens()
+    c = ffn_case(M, 256, 520, seed=M, mask=edge_mask(M, "alternating")).to(dev)
+    y_dec = _bf16_ffn_fused_forward(*c.apply_args())
+    y_gemm = _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)
+    check_status()
+    assert O.max_rel_err(y_dec, y_gemm.float()) < TOL
+
+
+@pytest.mark.parametrize("layout", ["T", "C"])
+def test_gateup_token_order_matches_reference_launcher(dev, layout):
+    # _bf16_ffn_forward (ffn_kernel/ffn.py:527-560) returns the [M, h] intermediate in token order
+    M, d, h = 700, 256, 392
+    c = ffn_case(M, d, h, seed=2, mask=edge_mask(M, "bernoulli", 2))
+    ref = O.masked_ffn_gateup(c.x, c.w1.T, c.w3.T, c.u1.T, c.u3.T, c.mask)
+    g = c.to(dev)
+    ws = [g.w1.T, g.w3.T, g.u1.T, g.u3.T]
+    if layout == "C":
+        ws = [w.contiguous() for w in ws]
+    out = _bf16_ffn_forward(g.x, *ws, g.mask)
+    check_status()
+    assert out.shape == (M, h)
+    assert O.max_rel_err(out, ref) < TOL
+
+
+def test_contiguous_weights(dev):
+    M, d, h = 600, 256, 392
+    c = ffn_case(M, d, h, seed=8, mask=edge_mask(M, "span", 1))
+    ref = O.masked_ffn(*c.apply_args())
+    g = c.to(dev)
+    args = [g.x] + [w.T.contiguous() for w in (g.w1, g.w2, g.w3, g.u1, g.u2, g.u3)] + [g.mask]
+    y = MaskedFFN.apply(*args)
+    check_status()
+    assert O.max_rel_err(y, ref) < TOL
+
+
+def test_tensor_parallel_slices_of_the_weight_views(dev):
+    # column slices of the [d, h] views and row slices of the [h, d] views are passed without copies;
+    # the partial results of the slices sum to the full result
+    M, d, h, P = 512, 256, 512, 4
+    c = ffn_case(M, d, h, seed=3)
+    ref = O.masked_ffn(*c.apply_args())
+    g = c.to(dev)
+    acc = torch.zeros(M, d, dtype=torch.float32, device=dev)
+    for r in range(P):
+        sl = slice(r * h // P, (r + 1) * h // P)
+        acc += MaskedFFN.apply(g.x, g.w1.T[:, sl], g.w2.T[sl, :], g.w3.T[:, sl], g.u1.T[:, sl], g.u2.T[sl, :],
+                               g.u3.T[:, sl], g.mask).float()
+    check_status()
+    assert O.max_rel_err(acc, ref) < TOL
+
+
+def test_backward_raises_like_the_reference(dev):
+    # ffn_kernel/ops.py:34-38
+    c = ffn_case(64, 64, 64, seed=1).to(dev)
+    x = c.x.clone().requires_grad_(True)
+    y = MaskedFFN.apply(x, *c.apply_args()[1:])
+    with pytest.raises(NotImplementedError):
+        y.sum().backward()
+
+
+def test_empty_input(dev):
+    c = ffn_case(8, 64, 64, seed=1).to(dev)
+    y = MaskedFFN.apply(c.x[:0], *c.apply_args()[1:7], c.mask[:0])
+    assert y.shape == (0, 64)
+
+
+def test_full_size_rows_sampled(dev):
+    # d = 4096 / h = 11008, M = 16384: 128 sampled rows against the oracle on those rows,
+    # plus row independence: the same rows computed alone give the same bits
+    M, d, h = 16384, 4096, 11008
+    c = ffn_case(M, d, h, seed=0)
+    g = c.to(dev)
+    y = MaskedFFN.apply(*g.apply_args())
+    check_status()
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:128]
+    ref = O.masked_ffn(c.x[rows], *c.apply_args()[1:7], c.mask[rows])
+    assert O.max_rel_err(y[rows.to(dev)], ref) < TOL
+    assert bool(torch.isfinite(y.float()).all())
+    sub = MaskedFFN.apply(g.x[rows.to(dev)], *g.apply_args()[1:7], g.mask[rows.to(dev)])
+    assert O.max_rel_err(sub, y[rows.to(dev)].float()) < 1e-2

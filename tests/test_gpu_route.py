@@ -1,0 +1,70 @@
+"""Routing kernel: bit-exact with nonzero(mask) / nonzero(~mask), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from ffn_kernel_b200 import check_status, route
+from ffn_kernel_b200.synth import edge_mask, span_mask
+from oracle import masked_ref as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(mask_cpu, dev):
+    rt = route(mask_cpu.to(dev))
+    check_status()
+    v, t = rt.lists()
+    ov, ot = O.routing(mask_cpu)
+    assert v.dtype == torch.int32 and t.dtype == torch.int32
+    assert np.array_equal(v.cpu().numpy(), ov)
+    assert np.array_equal(t.cpu().numpy(), ot)
+    assert rt.counts.tolist() == [len(ov), len(ot), rt.cap, mask_cpu.numel()]
+
+
+@pytest.mark.parametrize("M", [1, 2, 15, 16, 17, 127, 128, 129, 1000, 4095, 4096, 4097, 4099, 8192, 65537, 1 << 20])
+@pytest.mark.parametrize("kind", ["bernoulli", "all_visual", "all_text", "alternating", "span"])
+def test_route_bit_exact(dev, M, kind):
+    _check(edge_mask(M, kind, seed=M), dev)
+
+
+def test_route_uint8_mask_nonzero_is_visual(dev):
+    g = torch.Generator().manual_seed(0)
+    m = torch.randint(0, 4, (5000,), generator=g, dtype=torch.uint8)     # any non-zero byte selects
+    rt = route(m.to(dev))
+    v, t = rt.lists()
+    assert np.array_equal(v.cpu().numpy(), np.flatnonzero(m.numpy() != 0))
+    assert np.array_equal(t.cpu().numpy(), np.flatnonzero(m.numpy() == 0))
+
+
+def test_route_unaligned_view(dev):
+    base = edge_mask(10001, "bernoulli", 7)
+    view = base.to(dev)[1:]                       # data pointer not 16-byte aligned
+    rt = route(view)
+    v, t = rt.lists()
+    ov, ot = O.routing(base[1:])
+    assert np.array_equal(v.cpu().numpy(), ov) and np.array_equal(t.cpu().numpy(), ot)
+
+
+def test_route_empty(dev):
+    rt = route(torch.zeros(0, dtype=torch.bool, device=dev))
+    assert rt.counts.tolist()[:2] == [0, 0]
+
+
+def test_route_full_size_properties(dev):
+    # at benchmark sizes: the two lists are ascending, disjoint, and together a permutation
+    for M, seed in ((32768, 0), (16384, 0), (1 << 24, 1)):
+        m = (span_mask(M, seed) if M < (1 << 20) else edge_mask(M, "bernoulli", seed)).to(dev)
+        rt = route(m)
+        v, t = rt.lists()
+        assert bool((v[1:] > v[:-1]).all()) and bool((t[1:] > t[:-1]).all())
+        assert v.numel() + t.numel() == M
+        assert bool(m[v.long()].all()) and not bool(m[t.long()].any())
+        assert int(v.sum(dtype=torch.int64) + t.sum(dtype=torch.int64)) == M * (M - 1) // 2
+    check_status()
+
+
+def test_route_rejects_bad_arguments(dev):
+    with pytest.raises(RuntimeError):
+        route(torch.zeros(4, 4, dtype=torch.bool, device=dev))
+    with pytest.raises(RuntimeError):
+        route(torch.zeros(4, dtype=torch.float32, device=dev))
