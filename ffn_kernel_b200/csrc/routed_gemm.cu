@@ -21,6 +21,8 @@
 // under the main loop of tile i+1.
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "ffnk_internal.h"
 #include "ptx.cuh"
 
@@ -51,8 +53,46 @@ struct GemmParams {
   int k_len;            // contraction length
   int pad_row;          // row index fetched for the padding rows of a tile (>= M: zero fill)
   int group_m;          // m-tiles per super-tile of the tile order
+  int max_run_rows;     // largest tiled box used for runs of consecutive tokens (0: gather4 only)
   int* status;
 };
+
+// Views of one row-gathered activation matrix: m[0] fetches single rows (gather4); m[1 + i]
+// fetches boxes of 4 << i consecutive rows (4, 8, ..., 128), 64 columns wide.
+constexpr int RUN_LEVELS = 6;
+struct AMaps {
+  CUtensorMap m[1 + RUN_LEVELS];
+};
+
+// Run detection shared by the gathering producers.  Every lane holds four consecutive list
+// rows (r0..r3; `valid` = how many of them exist).  A block of 4n rows led by lane L (L a
+// multiple of n) can be fetched as one tiled box iff all its rows exist and are consecutive
+// tokens.  Returns, for this lane, the number of lanes n of the largest such aligned block
+// that contains the lane's rows (0 if not even its own four rows qualify); the lane with
+// (lane % n == 0) issues the box.  `lanes` is 32 (whole tile) or 16 (a 64-row k-step).
+__device__ __forceinline__ int run_block_lanes(int lane_in_group, int lanes, int r0, int r1, int r2, int r3, int valid,
+                                               int max_lanes) {
+  const int prev3 = __shfl_up_sync(0xFFFFFFFFu, r3, 1);
+  const bool s0 = (valid < 1) || (r0 != prev3 + 1);          // row 4l starts a new run (or is missing)
+  const bool s1 = (valid < 2) || (r1 != r0 + 1);
+  const bool s2 = (valid < 3) || (r2 != r1 + 1);
+  const bool s3 = (valid < 4) || (r3 != r2 + 1);
+  const uint32_t b0 = __ballot_sync(0xFFFFFFFFu, s0);
+  const uint32_t bi = __ballot_sync(0xFFFFFFFFu, s1 || s2 || s3);
+  const uint32_t bv = __ballot_sync(0xFFFFFFFFu, valid == 4);
+  const int shift = (threadIdx.x & 31) - lane_in_group;        // 0, or 16 for the upper half-warp
+  int best = 0;
+#pragma unroll
+  for (int n = 1; n <= 32; n <<= 1) {
+    if (n > lanes || n > max_lanes) break;
+    const int lead = lane_in_group & ~(n - 1);
+    const uint32_t range = (n == 32 ? 0xFFFFFFFFu : ((1u << n) - 1u) << lead) << shift;
+    const uint32_t inner = range & ~(1u << (lead + shift));
+    const bool ok = (bi & range) == 0 && (b0 & inner) == 0 && (bv & range) == range;
+    if (ok) best = n;
+  }
+  return best;
+}
 
 struct TileCoord {
   int mt, nt;           // m-tile over [visual tiles | text tiles], n-tile
@@ -97,8 +137,7 @@ __device__ __forceinline__ float silu_mul(float t1, float t3) {
 
 template <int A_MODE, int EPI, int OUT_MODE, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA32,
-                   const __grid_constant__ CUtensorMap tmA128, const __grid_constant__ CUtensorMap tmBv0,
+routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUtensorMap tmBv0,
                    const __grid_constant__ CUtensorMap tmBv1, const __grid_constant__ CUtensorMap tmBt0,
                    const __grid_constant__ CUtensorMap tmBt1, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -124,9 +163,7 @@ routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
     *abort_flag = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmA32);
-    tma_prefetch_desc(&tmA128);
+    for (int i = 0; i <= RUN_LEVELS; ++i) tma_prefetch_desc(&am.m[i]);
     tma_prefetch_desc(&tmBv0);
     tma_prefetch_desc(&tmBv1);
     tma_prefetch_desc(&tmBt0);
@@ -158,27 +195,23 @@ routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_v, m_tiles, n_tiles, p.group_m, Mv, Mt, cap);
       int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
-      // How this lane's rows are fetched: 0 = gather4 of its four rows, 1 = its 32-row quarter of
-      // the tile is one run of consecutive tokens (one tiled box per quarter), 2 = the whole tile is.
-      int run_mode = 0;
+      // How this lane's rows are fetched: as part of a tiled box of 4 * run_lanes consecutive
+      // token rows issued by the block's first lane, or (run_lanes == 0) by a gather4 of its own.
+      int run_lanes = 0;
       if constexpr (A_MODE == A_GATHER) {
         const int lr = 4 * lane;  // first of this lane's four rows
-        if (lr < tc.rows) {
+        const int valid = min(4, max(0, tc.rows - lr));
+        if (valid > 0) {
           const int4 v = *reinterpret_cast<const int4*>(p.perm + tc.list_off + tc.row0 + lr);
           r0 = v.x;
-          if (lr + 1 < tc.rows) r1 = v.y;
-          if (lr + 2 < tc.rows) r2 = v.z;
-          if (lr + 3 < tc.rows) r3 = v.w;
+          if (valid > 1) r1 = v.y;
+          if (valid > 2) r2 = v.z;
+          if (valid > 3) r3 = v.w;
         }
-        const bool lane_run = (lr + 3 < tc.rows) && r1 == r0 + 1 && r2 == r0 + 2 && r3 == r0 + 3;
-        const int qbase = __shfl_sync(0xFFFFFFFFu, r0, lane & ~7);
-        const int tbase = __shfl_sync(0xFFFFFFFFu, r0, 0);
-        const uint32_t q_ball = __ballot_sync(0xFFFFFFFFu, lane_run && r0 == qbase + 4 * (lane & 7));
-        const uint32_t t_ball = __ballot_sync(0xFFFFFFFFu, lane_run && r0 == tbase + lr);
-        const uint32_t q_bits = 0xFFu << (lane & ~7);
-        if (t_ball == 0xFFFFFFFFu) run_mode = 2;
-        else if ((q_ball & q_bits) == q_bits) run_mode = 1;
+        run_lanes = run_block_lanes(lane, 32, r0, r1, r2, r3, valid, p.max_run_rows >> 2);
       }
+      const bool run_lead = run_lanes > 0 && (lane & (run_lanes - 1)) == 0;
+      const CUtensorMap* run_map = &am.m[run_lanes > 0 ? 32 - __clz(run_lanes) : 0];
       const CUtensorMap* mB0 = tc.text ? &tmBt0 : &tmBv0;
       const CUtensorMap* mB1 = tc.text ? &tmBt1 : &tmBv1;
       for (int ks = 0; ks < k_steps; ++ks) {
@@ -196,15 +229,10 @@ routed_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         __syncwarp();
         const int kx = ks * BK;
         if constexpr (A_MODE == A_GATHER) {
-          if (run_mode == 2) {
-            if (lane == 0) tma_load_2d(sa, &tmA128, &full[stage], kx, r0);
-          } else if (run_mode == 1) {
-            if ((lane & 7) == 0) tma_load_2d(sa + lane * 512, &tmA32, &full[stage], kx, r0);
-          } else {
-            tma_gather4(sa + lane * 512, &tmA, &full[stage], kx, r0, r1, r2, r3);
-          }
+          if (run_lanes == 0) tma_gather4(sa + lane * 512, &am.m[0], &full[stage], kx, r0, r1, r2, r3);
+          else if (run_lead) tma_load_2d(sa + lane * 512, run_map, &full[stage], kx, r0);
         } else {
-          if (lane == 0) tma_load_2d(sa, &tmA, &full[stage], kx, tc.mt * BM);
+          if (lane == 0) tma_load_2d(sa, &am.m[RUN_LEVELS], &full[stage], kx, tc.mt * BM);
         }
         if (lane == 0) {
           if constexpr (!B_MN) {
@@ -388,6 +416,7 @@ struct WgradParams {
   int p_dim;      // output rows    (columns of P)
   int q_dim;      // output columns (columns of Q)
   int pad_row;
+  int max_run_rows;
   int* status;
 };
 
@@ -412,9 +441,7 @@ __device__ __forceinline__ WgradTile decode_wgrad_tile(int t, int p_tiles, int q
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-             const __grid_constant__ CUtensorMap tmP32, const __grid_constant__ CUtensorMap tmQ32,
-             const WgradParams p) {
+wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm, const WgradParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -438,10 +465,10 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CU
     }
     *abort_flag = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&tmP);
-    tma_prefetch_desc(&tmQ);
-    tma_prefetch_desc(&tmP32);
-    tma_prefetch_desc(&tmQ32);
+    for (int i = 0; i < RUN_LEVELS; ++i) {
+      tma_prefetch_desc(&pm.m[i]);
+      tma_prefetch_desc(&qm.m[i]);
+    }
   }
   if (warp == 1) {
     tmem_alloc<1>(tmem_slot, TMEM_COLS);
@@ -478,18 +505,17 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CU
         // the next k-step's rows are requested now so that the load is hidden behind this step
         if (ks + 1 < k_steps) nxt = (lr + BK < wt.cnt) ? *reinterpret_cast<const int4*>(list + lr + BK) : pad4;
         int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
-        if (lr < wt.cnt) {
+        const int valid = min(4, max(0, wt.cnt - lr));
+        if (valid > 0) {
           r0 = v.x;
-          if (lr + 1 < wt.cnt) r1 = v.y;
-          if (lr + 2 < wt.cnt) r2 = v.z;
-          if (lr + 3 < wt.cnt) r3 = v.w;
+          if (valid > 1) r1 = v.y;
+          if (valid > 2) r2 = v.z;
+          if (valid > 3) r3 = v.w;
         }
-        // 32 list rows that are consecutive tokens are fetched as one tiled box per column block
-        const bool lane_run = (lr + 3 < wt.cnt) && r1 == r0 + 1 && r2 == r0 + 2 && r3 == r0 + 3;
-        const int hbase = __shfl_sync(0xFFFFFFFFu, r0, lane & ~7);
-        const uint32_t ball = __ballot_sync(0xFFFFFFFFu, lane_run && r0 == hbase + 4 * (lane & 7));
-        const uint32_t bits = 0xFFu << (lane & ~7);
-        const bool run = (ball & bits) == bits;
+        // list rows that are consecutive tokens are fetched as tiled boxes of 4..64 rows per column block
+        const int run_lanes = run_block_lanes(gi, 16, r0, r1, r2, r3, valid, p.max_run_rows >> 2);
+        const bool run_lead = run_lanes > 0 && (gi & (run_lanes - 1)) == 0;
+        const int level = run_lanes > 0 ? 32 - __clz(run_lanes) : 0;
         int w = 1;
         if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
         w = __shfl_sync(0xFFFFFFFFu, w, 0);
@@ -507,16 +533,14 @@ wgrad_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CU
         uint8_t* dq0 = sq + half * 8192 + gi * 512;
         uint8_t* dq1 = sq + (2 + half) * 8192 + gi * 512;
         const int cp = wt.pt * BM + half * 64, cq0 = wt.qt * BN + half * 64, cq1 = wt.qt * BN + (2 + half) * 64;
-        if (run) {
-          if ((lane & 7) == 0) {
-            tma_load_2d(dp, &tmP32, &full[stage], cp, r0);
-            tma_load_2d(dq0, &tmQ32, &full[stage], cq0, r0);
-            tma_load_2d(dq1, &tmQ32, &full[stage], cq1, r0);
-          }
-        } else {
-          tma_gather4(dp, &tmP, &full[stage], cp, r0, r1, r2, r3);
-          tma_gather4(dq0, &tmQ, &full[stage], cq0, r0, r1, r2, r3);
-          tma_gather4(dq1, &tmQ, &full[stage], cq1, r0, r1, r2, r3);
+        if (run_lanes == 0) {
+          tma_gather4(dp, &pm.m[0], &full[stage], cp, r0, r1, r2, r3);
+          tma_gather4(dq0, &qm.m[0], &full[stage], cq0, r0, r1, r2, r3);
+          tma_gather4(dq1, &qm.m[0], &full[stage], cq1, r0, r1, r2, r3);
+        } else if (run_lead) {
+          tma_load_2d(dp, &pm.m[level], &full[stage], cp, r0);
+          tma_load_2d(dq0, &qm.m[level], &full[stage], cq0, r0);
+          tma_load_2d(dq1, &qm.m[level], &full[stage], cq1, r0);
         }
         ++issued;
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -662,13 +686,19 @@ static int weight_map(CUtensorMap* m, const WeightView& w, bool* mn_major) {
   return FFNK_ERR_LAYOUT;
 }
 
-// The three views of a row-gathered activation matrix [rows, cols]: single rows for gather4,
-// and 32- and 128-row boxes for the parts of a tile that are runs of consecutive tokens.
-static int gather_maps(CUtensorMap (&m)[3], const void* base, int64_t cols, int64_t rows, int64_t ld) {
-  int r = make_tensor_map_2d(&m[0], base, cols, rows, ld, BK, 1);
-  if (r) return r;
-  if ((r = make_tensor_map_2d(&m[1], base, cols, rows, ld, BK, 32))) return r;
-  return make_tensor_map_2d(&m[2], base, cols, rows, ld, BK, BM);
+static int gather_maps(AMaps& a, const void* base, int64_t cols, int64_t rows, int64_t ld) {
+  int r = make_tensor_map_2d(&a.m[0], base, cols, rows, ld, BK, 1);
+  for (int i = 0; i < RUN_LEVELS && !r; ++i) r = make_tensor_map_2d(&a.m[1 + i], base, cols, rows, ld, BK, 4u << i);
+  return r;
+}
+
+// Largest run box in rows; FFNK_MAX_RUN_ROWS (0, 4, 8, ..., 128) overrides it for experiments.
+static int max_run_rows() {
+  static const int v = [] {
+    const char* e = getenv("FFNK_MAX_RUN_ROWS");
+    return e ? atoi(e) : BM;
+  }();
+  return v;
 }
 
 static int pick_group_m(int64_t k_len) {
@@ -681,7 +711,7 @@ static int pick_group_m(int64_t k_len) {
 }
 
 template <int A_MODE, int EPI, int OUT_MODE>
-static int launch_gemm(const CUtensorMap (&tmA)[3], const CUtensorMap (&tmB)[4], bool b_mn, const GemmParams& p,
+static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn, const GemmParams& p,
                        int64_t m_tiles_max, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
@@ -693,8 +723,7 @@ static int launch_gemm(const CUtensorMap (&tmA)[3], const CUtensorMap (&tmB)[4],
   auto go = [&](auto kernel) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return cuda_status(e);
-    kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, stream>>>(tmA[0], tmA[1], tmA[2], tmB[0], tmB[1],
-                                                                             tmB[2], tmB[3], p);
+    kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
     return cuda_status(cudaGetLastError());
   };
   return b_mn ? go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, true>)
@@ -714,7 +743,8 @@ extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const
   if (!a || !b1 || !b2 || !perm || !counts || !c) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(N) || bad_dim(K)) return FFNK_ERR_SHAPE;
   if ((lda & 7) || (ldc & 7) || lda < K || ldc < N || (reinterpret_cast<uintptr_t>(c) & 15)) return FFNK_ERR_ALIGN;
-  CUtensorMap tmA[3], tmB[4];
+  AMaps tmA;
+  CUtensorMap tmB[4];
   int r = gather_maps(tmA, a, K, M, lda);
   if (r) return r;
   bool mn1 = false, mn2 = false;
@@ -723,7 +753,7 @@ extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const
   tmB[1] = tmB[0];
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(c), ldc, static_cast<int>(N), static_cast<int>(K),
-               static_cast<int>(M), pick_group_m(K), status};
+               static_cast<int>(M), pick_group_m(K), max_run_rows(), status};
   return launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1,
                                                        static_cast<cudaStream_t>(stream));
 }
@@ -736,7 +766,8 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
   if (!x || !w1 || !w3 || !u1 || !u3 || !perm || !counts || !out) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
   if ((ldx & 7) || (ldo & 7) || ldx < d || ldo < h || (reinterpret_cast<uintptr_t>(out) & 15)) return FFNK_ERR_ALIGN;
-  CUtensorMap tmA[3], tmB[4];
+  AMaps tmA;
+  CUtensorMap tmB[4];
   int r = gather_maps(tmA, x, d, M, ldx);
   if (r) return r;
   bool mn = false, mn_i = false;
@@ -746,7 +777,7 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
     mn = mn_i;
   }
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(out), ldo, static_cast<int>(h), static_cast<int>(d),
-               static_cast<int>(M), pick_group_m(d), status};
+               static_cast<int>(M), pick_group_m(d), max_run_rows(), status};
   const int64_t mt = (M + BM - 1) / BM + 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return routed_out ? launch_gemm<A_GATHER, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, mt, s)
@@ -761,17 +792,18 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
   if ((ldi & 7) || (ldy & 7) || ldi < h || ldy < d || (reinterpret_cast<uintptr_t>(y) & 15)) return FFNK_ERR_ALIGN;
   const int64_t rows = ffnk_route_capacity(M) + BM;
-  CUtensorMap tmA[3], tmB[4];
-  int r = make_tensor_map_2d(&tmA[0], inter, h, rows, ldi, BK, BM);
+  AMaps tmA;
+  CUtensorMap tmB[4];
+  int r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], inter, h, rows, ldi, BK, BM);
   if (r) return r;
-  tmA[1] = tmA[2] = tmA[0];
+  for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
   bool mn1 = false, mn2 = false;
   if ((r = weight_map(&tmB[0], WeightView{w2, w_stride_k, w_stride_n, h, d}, &mn1))) return r;
   if ((r = weight_map(&tmB[2], WeightView{u2, w_stride_k, w_stride_n, h, d}, &mn2))) return r;
   tmB[1] = tmB[0];
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(y), ldy, static_cast<int>(d), static_cast<int>(h),
-               static_cast<int>(M), pick_group_m(h), status};
+               static_cast<int>(M), pick_group_m(h), max_run_rows(), status};
   return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1,
                                                        static_cast<cudaStream_t>(stream));
 }
@@ -803,7 +835,8 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
 
   // dx: the forward kernel on g with the weights seen as [N, K] (contraction over N)
   {
-    CUtensorMap tmA[3], tmB[4];
+    AMaps tmA;
+    CUtensorMap tmB[4];
     int r = gather_maps(tmA, g, N, M, ldg);
     if (r) return r;
     bool mn1 = false, mn2 = false;
@@ -812,7 +845,7 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     tmB[1] = tmB[0];
     tmB[3] = tmB[2];
     GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(da), ldda, static_cast<int>(K), static_cast<int>(N),
-                 static_cast<int>(M), pick_group_m(N), status};
+                 static_cast<int>(M), pick_group_m(N), max_run_rows(), status};
     r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1, s);
     if (r) return r;
   }
@@ -822,20 +855,18 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     const void* Q = k_major ? a : g;
     const int64_t ldp = k_major ? ldg : lda, ldq = k_major ? lda : ldg;
     const int64_t p_dim = k_major ? N : K, q_dim = k_major ? K : N;
-    CUtensorMap tmP, tmQ, tmP32, tmQ32;
-    int r = make_tensor_map_2d(&tmP, P, p_dim, M, ldp, 64, 1);
+    AMaps tmP, tmQ;
+    int r = gather_maps(tmP, P, p_dim, M, ldp);
     if (r) return r;
-    if ((r = make_tensor_map_2d(&tmQ, Q, q_dim, M, ldq, 64, 1))) return r;
-    if ((r = make_tensor_map_2d(&tmP32, P, p_dim, M, ldp, 64, 32))) return r;
-    if ((r = make_tensor_map_2d(&tmQ32, Q, q_dim, M, ldq, 64, 32))) return r;
+    if ((r = gather_maps(tmQ, Q, q_dim, M, ldq))) return r;
     WgradParams wp{perm, counts, static_cast<__nv_bfloat16*>(db1), static_cast<__nv_bfloat16*>(db2),
                    k_major ? b_stride_n : b_stride_k, static_cast<int>(p_dim), static_cast<int>(q_dim),
-                   static_cast<int>(M), status};
+                   static_cast<int>(M), max_run_rows() < 64 ? max_run_rows() : 64, status};
     int64_t grid = 2 * ((p_dim + BM - 1) / BM) * ((q_dim + BN - 1) / BN);
     if (grid > dev.sm_count) grid = dev.sm_count;
     cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return cuda_status(e);
-    wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, tmP32, tmQ32, wp);
+    wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
     return cuda_status(cudaGetLastError());
   }
 }
