@@ -1,0 +1,127 @@
+"""Per-kernel timing sweep: the tool behind the tile table and the summaries in profiles/.
+
+    python -m ffn_kernel_b200.sweep ffn      --M 16384 --d 4096 --h 11008 [--mask span]
+    python -m ffn_kernel_b200.sweep linear   --M 32768 --K 4096 --N 4096 [--mask span] [--bwd]
+    python -m ffn_kernel_b200.sweep route    --M 67108864
+    python -m ffn_kernel_b200.sweep decode   --M 8 --d 1024 --h 2816 [--mask alternating]
+
+Each kernel is launched through the C ABI and timed with CUDA events on the launching stream
+(warm-up first, inputs larger than L2 or rotated over several copies).  One JSON line per kernel.
+The environment variable FFNK_MAX_RUN_ROWS (0, 4, 8, ..., 128) caps the height of the tiled TMA
+boxes used for runs of consecutive tokens; 0 forces gather4 everywhere.  It replaces the reference's
+offline search (``find_spec/find.py:18-64``): there is nothing to search, only choices to measure.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import check_status, route
+from ._lib import lib
+from .ffn import _bf16_ffn_fused_forward
+from .linear import _bf16_linear_backward, _bf16_linear_forward
+from .route import status_word, stream_ptr
+from .synth import edge_mask, ffn_case, linear_case
+
+
+def timeit(fn, iters: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def emit(**kw):
+    kw["max_run_rows"] = os.environ.get("FFNK_MAX_RUN_ROWS", "128")
+    print(json.dumps(kw), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["ffn", "linear", "route", "decode", "once"])
+    ap.add_argument("--M", type=int, default=16384)
+    ap.add_argument("--d", type=int, default=4096)
+    ap.add_argument("--h", type=int, default=11008)
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--N", type=int, default=4096)
+    ap.add_argument("--mask", default="span")
+    ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    L = lib()
+    st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
+
+    if a.what in ("ffn", "once"):
+        M, d, h = a.M, a.d, a.h
+        c = ffn_case(M, d, h, seed=0, mask=edge_mask(M, a.mask, 0)).to(dev)
+        if a.what == "once":          # a couple of plain forward passes: the command ncu captures
+            for _ in range(2):
+                _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)
+            torch.cuda.synchronize()
+            check_status()
+            return
+        rt = route(c.mask)
+        inter = torch.empty((rt.cap + 128, h), device=dev, dtype=torch.bfloat16)
+        y = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
+
+        def gateup():
+            L.ffnk_ffn_gateup(c.x.data_ptr(), d, c.w1.data_ptr(), c.w3.data_ptr(), c.u1.data_ptr(), c.u3.data_ptr(),
+                              1, d, rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), h, 1, M, d, h, st, sp)
+
+        def down():
+            L.ffnk_ffn_down(inter.data_ptr(), h, c.w2.data_ptr(), c.u2.data_ptr(), 1, h, rt.perm.data_ptr(),
+                            rt.counts.data_ptr(), y.data_ptr(), d, M, d, h, st, sp)
+
+        t = timeit(gateup, a.iters, a.warmup)
+        emit(kernel="ffn_gateup", M=M, d=d, h=h, mask=a.mask, ms=t, tflops=4 * M * d * h / t / 1e9)
+        t = timeit(down, a.iters, a.warmup)
+        emit(kernel="ffn_down", M=M, d=d, h=h, mask=a.mask, ms=t, tflops=2 * M * d * h / t / 1e9)
+        t = timeit(lambda: _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False), a.iters, a.warmup)
+        emit(kernel="ffn_forward(route+gateup+down)", M=M, d=d, h=h, mask=a.mask, ms=t,
+             tflops=6 * M * d * h / t / 1e9)
+    elif a.what == "linear":
+        M, K, N = a.M, a.K, a.N
+        c = linear_case(M, K, N, seed=0, mask=edge_mask(M, a.mask, 0), with_grad=True).to(dev)
+        rt = route(c.mask)
+        t = timeit(lambda: _bf16_linear_forward(c.x, c.wv.T, c.wt.T, c.mask, rt), a.iters, a.warmup)
+        emit(kernel="linear_fwd", M=M, K=K, N=N, mask=a.mask, ms=t, tflops=2 * M * K * N / t / 1e9)
+        if a.bwd:
+            t = timeit(lambda: _bf16_linear_backward(c.g, c.x, c.wv.T, c.wt.T, c.mask, rt), a.iters, a.warmup)
+            emit(kernel="linear_bwd(dx+dW)", M=M, K=K, N=N, mask=a.mask, ms=t, tflops=4 * M * K * N / t / 1e9)
+    elif a.what == "route":
+        m = edge_mask(a.M, "bernoulli" if a.mask == "span" and a.M > (1 << 22) else a.mask, 0).to(dev)
+        t = timeit(lambda: route(m), a.iters, a.warmup)
+        emit(kernel="route", M=a.M, ms=t, gbs=5 * a.M / t / 1e6)
+    elif a.what == "decode":
+        M, d, h = a.M, a.d, a.h
+        # rotate over enough weight sets that the stream comes from HBM, not from L2
+        n_sets = max(2, int(300e6 // (6 * d * h * 2)) + 1)
+        cases = [ffn_case(M, d, h, seed=s, mask=edge_mask(M, a.mask, 0)).to(dev) for s in range(n_sets)]
+        args = [cs.apply_args() for cs in cases]
+        g = torch.cuda.CUDAGraph()
+        for ar in args:
+            _bf16_ffn_fused_forward(*ar)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            for ar in args:
+                _bf16_ffn_fused_forward(*ar)
+        t = timeit(g.replay, a.iters, a.warmup) / n_sets
+        present = (1 if bool(cases[0].mask.any()) else 0) + (1 if bool((~cases[0].mask).any()) else 0)
+        emit(kernel="ffn_decode(2 launches)", M=M, d=d, h=h, mask=a.mask, ms=t, weight_sets=n_sets,
+             gbs=present * 3 * d * h * 2 / t / 1e6)
+    check_status()
+
+
+if __name__ == "__main__":
+    main()
