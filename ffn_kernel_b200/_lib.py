@@ -20,6 +20,7 @@ SIGNATURES = {
     "ffnk_route_capacity": (c_int64, [c_int64]),
     "ffnk_route_workspace_bytes": (c_int64, [c_int64]),
     "ffnk_route": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ffnk_route_noalloc": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ffnk_linear_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
                                 c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "ffnk_linear_bwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,

@@ -128,6 +128,7 @@ extern "C" const char* ffnk_status_string(int code) {
     case FFNK_ERR_DRIVER: return "cuTensorMapEncodeTiled driver entry point unavailable";
     case FFNK_ERR_TENSORMAP: return "tensor map rejected by the driver";
     case FFNK_ERR_DEVICE: return "device is not compute capability 10.x";
+    case FFNK_ERR_CAPACITY: return "problem exceeds the fixed capacity of the no-allocation entry point";
     case ST_TIMEOUT_PRODUCER: return "device: TMA producer wait expired";
     case ST_TIMEOUT_MMA_FULL: return "device: MMA wait for operands expired";
     case ST_TIMEOUT_MMA_TMEM: return "device: MMA wait for accumulator expired";

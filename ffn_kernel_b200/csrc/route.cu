@@ -13,6 +13,8 @@
 // tile's predecessors have always started; the look-back spin is bounded all the same.
 //
 // Algorithmic traffic: 1 byte read + 4 bytes written per token.
+#include <mutex>
+
 #include "ffnk_internal.h"
 #include "ptx.cuh"
 
@@ -184,5 +186,70 @@ extern "C" int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* c
   if (e != cudaSuccess) return cuda_status(e);
   route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,
                                                     counts, static_cast<uint32_t*>(workspace), status);
+  return cuda_status(cudaGetLastError());
+}
+
+// -------------------------------------------------------------------------------------------
+// Routing without any allocation by anybody.
+//
+// ffnk_route() needs a few kilobytes of scan state that the caller has to allocate.  Some hosts
+// cannot do that at the point where they call us: an inference-server or runtime plugin whose
+// execute callback is given all its buffers up front and is forbidden to allocate device memory,
+// or a steady-state serving loop that must not touch cudaMalloc because it synchronises the
+// whole device.  For them the scan state lives in the fixed array below.  It is part of the
+// library image, so every GPU that loads the library carries these 16.25 KiB until the process
+// exits, and it bounds the mask length at FFNK_ROUTE_NOALLOC_MAX_TOKENS.
+// -------------------------------------------------------------------------------------------
+namespace ffnk {
+constexpr int64_t kNoAllocMaxTokens = FFNK_ROUTE_NOALLOC_MAX_TOKENS;
+constexpr int64_t kNoAllocWords = 1 + (kNoAllocMaxTokens + kRouteTile - 1) / kRouteTile;   // ticket + tile states
+constexpr int64_t kNoAllocWordsPadded = ((kNoAllocWords + 63) / 64) * 64;
+
+static __device__ __align__(256) uint32_t g_route_scratch[kNoAllocWordsPadded];
+
+// In host code `g_route_scratch` is only a handle for the runtime, not an address a kernel can
+// use: the device address is asked for once per device (with that device current) and cached.
+static int route_scratch_address(uint32_t** out) {
+  static std::mutex mu;
+  static uint32_t* addr[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (dev < 0 || dev >= 64) return FFNK_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    uint32_t* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_route_scratch);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (ptr == nullptr) return FFNK_ERR_DEVICE;
+    addr[dev] = ptr;
+  }
+  *out = addr[dev];
+  return 0;
+}
+}  // namespace ffnk
+
+extern "C" int ffnk_route_noalloc(const void* mask, int64_t M, int32_t* perm, int32_t* counts, int32_t* status,
+                                  void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0) return FFNK_ERR_SHAPE;
+  if (M > kNoAllocMaxTokens) return FFNK_ERR_CAPACITY;
+  if (!counts || !status) return FFNK_ERR_NULL;
+  const int cap = static_cast<int>(ffnk_route_capacity(M));
+  if (M == 0) {
+    route_empty_kernel<<<1, 1, 0, stream>>>(counts, cap);
+    return cuda_status(cudaGetLastError());
+  }
+  if (!mask || !perm) return FFNK_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(perm) & 15) return FFNK_ERR_ALIGN;
+  uint32_t* scratch = nullptr;
+  const int r = route_scratch_address(&scratch);
+  if (r) return r;
+  const int tiles = static_cast<int>((M + kRouteTile - 1) / kRouteTile);
+  // the array still holds the previous call's ticket and tile states: clear the part this call uses
+  cudaError_t e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(tiles) + 1) * sizeof(uint32_t), stream);
+  if (e != cudaSuccess) return cuda_status(e);
+  route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,
+                                                    counts, scratch, status);
   return cuda_status(cudaGetLastError());
 }

@@ -40,6 +40,7 @@ extern "C" {
 #define FFNK_ERR_DRIVER (-5)    /* the CUDA driver entry point for tensor maps is unavailable */
 #define FFNK_ERR_TENSORMAP (-6) /* the driver rejected a tensor map */
 #define FFNK_ERR_DEVICE (-7)    /* the current device is not compute capability 10.x */
+#define FFNK_ERR_CAPACITY (-8)  /* the problem exceeds the fixed capacity of a no-allocation entry point */
 
 /* Library version (major * 100 + minor). */
 int ffnk_version(void);
@@ -59,6 +60,26 @@ int64_t ffnk_route_capacity(int64_t M);
 int64_t ffnk_route_workspace_bytes(int64_t M);
 int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* counts, void* workspace, int32_t* status,
                void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Routing for callers that cannot provide scratch memory.  This entry point has no counterpart
+ * in the reference; it exists for hosts that must not allocate when they call: a serving-runtime
+ * plugin whose execute callback gets every buffer up front and may not allocate device memory,
+ * or a steady-state loop that avoids cudaMalloc because it synchronises the device.
+ *
+ * Same results as ffnk_route() (perm, counts as described above) but without the workspace
+ * argument: the scan state lives in a fixed 16.25 KiB array inside the library, which every GPU
+ * that loads the library keeps until the process exits.  Consequences:
+ *   - M may not exceed FFNK_ROUTE_NOALLOC_MAX_TOKENS; a longer mask returns FFNK_ERR_CAPACITY
+ *     and launches nothing.
+ *   - All calls on a device share that one array (each call clears the part it uses), so two
+ *     calls that may run on the GPU at the same time -- different streams -- race.  Issue them
+ *     on one stream, or order them with events.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     outside any stream capture.  Nothing is allocated or freed, then or later.
+ * ------------------------------------------------------------------------------------- */
+#define FFNK_ROUTE_NOALLOC_MAX_TOKENS 16777216 /* 2^24 tokens */
+int ffnk_route_noalloc(const void* mask, int64_t M, int32_t* perm, int32_t* counts, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * MaskedLinear forward.  Replaces _bf16_linear_forward (ffn_kernel/linear.py:418-452) and
