@@ -135,6 +135,66 @@ __device__ __forceinline__ float silu_mul(float t1, float t3) {
   return t1 * __frcp_rn(1.0f + __expf(-t1)) * t3;
 }
 
+
+// Rows of the routed intermediate: visual rows start at 0, text rows at the next multiple of
+// 256 after the visual rows (the largest row tile any kernel variant uses).
+__device__ __forceinline__ int text_row_base(int Mv) { return ((Mv + 255) >> 8) << 8; }
+
+// Epilogue of one accumulator row: this thread owns TMEM lane `taddr`'s row, 256 fp32 columns.
+// EPI_STORE : out_row[n_base + c] = bf16(acc[c]),                       256 columns
+// EPI_SWIGLU: out_row[n_base + c] = bf16(silu(acc[c]) * acc[128 + c]),   128 columns
+template <int EPI>
+__device__ __forceinline__ void epilogue_row(uint32_t taddr, __nv_bfloat16* out_row, bool valid, int n_base,
+                                             int n_out) {
+  if constexpr (EPI == EPI_STORE) {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t v[32];
+      tmem_ld_32x32(taddr + c * 32, v);
+      tmem_ld_wait();
+      const int n0 = n_base + c * 32;
+      if (valid && n0 < n_out) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (n0 + j * 8 < n_out) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
+            o.y = pack_bf16(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
+            o.z = pack_bf16(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
+            o.w = pack_bf16(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
+            *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN / 64; ++c) {
+      uint32_t g[32], u[32];
+      tmem_ld_32x32(taddr + c * 32, g);            // gate  (t1)
+      tmem_ld_32x32(taddr + BN / 2 + c * 32, u);   // up    (t3)
+      tmem_ld_wait();
+      const int n0 = n_base + c * 32;
+      if (valid && n0 < n_out) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (n0 + j * 8 < n_out) {
+            float h[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) h[e] = silu_mul(__uint_as_float(g[j * 8 + e]), __uint_as_float(u[j * 8 + e]));
+            uint4 o;
+            o.x = pack_bf16(h[0], h[1]);
+            o.y = pack_bf16(h[2], h[3]);
+            o.z = pack_bf16(h[4], h[5]);
+            o.w = pack_bf16(h[6], h[7]);
+            *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int A_MODE, int EPI, int OUT_MODE, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUtensorMap tmBv0,
@@ -232,7 +292,8 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
           if (run_lanes == 0) tma_gather4(sa + lane * 512, &am.m[0], &full[stage], kx, r0, r1, r2, r3);
           else if (run_lead) tma_load_2d(sa + lane * 512, run_map, &full[stage], kx, r0);
         } else {
-          if (lane == 0) tma_load_2d(sa, &am.m[RUN_LEVELS], &full[stage], kx, tc.mt * BM);
+          if (lane == 0)
+            tma_load_2d(sa, &am.m[RUN_LEVELS], &full[stage], kx, (tc.text ? text_row_base(Mv) : 0) + tc.row0);
         }
         if (lane == 0) {
           if constexpr (!B_MN) {
@@ -319,7 +380,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       int64_t dst_row = 0;
       if (valid) {
         if constexpr (OUT_MODE == OUT_SCATTER) dst_row = p.perm[tc.list_off + tc.row0 + row];
-        else dst_row = static_cast<int64_t>(tc.mt) * BM + row;
+        else dst_row = static_cast<int64_t>(tc.text ? text_row_base(Mv) : 0) + tc.row0 + row;
       }
       int w = 1;
       if (lane == 0) w = mbar_wait(&tfull[acc], acc_phase, abort_flag) ? 1 : 0;
@@ -331,56 +392,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       __nv_bfloat16* out_row = p.out + dst_row * p.ldo;
-      if constexpr (EPI == EPI_STORE) {
-        const int n_base = tc.nt * BN;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c * 32, v);
-          tmem_ld_wait();
-          const int n0 = n_base + c * 32;
-          if (valid && n0 < p.n_out) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (n0 + j * 8 < p.n_out) {
-                uint4 o;
-                o.x = pack_bf16(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
-                o.y = pack_bf16(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
-                o.z = pack_bf16(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
-                o.w = pack_bf16(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
-                *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
-              }
-            }
-          }
-        }
-      } else {
-        const int n_base = tc.nt * (BN / 2);
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(taddr + c * 32, g);            // gate  (t1)
-          tmem_ld_32x32(taddr + BN / 2 + c * 32, u);   // up    (t3)
-          tmem_ld_wait();
-          const int n0 = n_base + c * 32;
-          if (valid && n0 < p.n_out) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (n0 + j * 8 < p.n_out) {
-                float h[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  h[e] = silu_mul(__uint_as_float(g[j * 8 + e]), __uint_as_float(u[j * 8 + e]));
-                uint4 o;
-                o.x = pack_bf16(h[0], h[1]);
-                o.y = pack_bf16(h[2], h[3]);
-                o.z = pack_bf16(h[4], h[5]);
-                o.w = pack_bf16(h[6], h[7]);
-                *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
-              }
-            }
-          }
-        }
-      }
+      epilogue_row<EPI>(taddr, out_row, valid, tc.nt * (EPI == EPI_SWIGLU ? BN / 2 : BN), p.n_out);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -393,6 +405,248 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+
+// -------------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster (the two SMs of one TPC) share one
+// tcgen05.mma.cta_group::2 of 256 x 256 x 16.  Each CTA fetches its own 128 tile rows of A and
+// only HALF of the B tile (128 of the 256 weight rows), so a k-step moves 32 KiB per SM instead
+// of 48 and needs two TMA instructions instead of three; six stages fit where four did.
+//   * the even CTA (the leader) issues every MMA; its `full` barriers collect the byte counts
+//     of both CTAs' loads (the partner's TMA credits the leader's barrier directly);
+//   * tcgen05.commit with a two-CTA mask frees the stage in both CTAs and hands the finished
+//     accumulator (128 lanes x 256 columns in each CTA's TMEM) to both epilogues;
+//   * both CTAs' epilogue warps report back to the leader's `tempty` barrier.
+// In the gate/up kernel the leader's B half is the gate weight slice and the partner's the up
+// slice, so each CTA's accumulator is again 128 gate columns | 128 up columns.
+// -------------------------------------------------------------------------------------------
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_B_BYTES = B_BYTES / 2;                       // 16 KiB: this CTA's half of B
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;        // 32 KiB
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+constexpr int PAIR_BM = 2 * BM;                                 // 256 tile rows per pair
+
+template <int A_MODE, int EPI, int OUT_MODE, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUtensorMap tmBv0,
+                        const __grid_constant__ CUtensorMap tmBv1, const __grid_constant__ CUtensorMap tmBt0,
+                        const __grid_constant__ CUtensorMap tmBt1, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES);
+  uint64_t* empty = full + PAIR_STAGES;
+  uint64_t* tfull = empty + PAIR_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();        // 0 = leader
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full[s], 2);      // one arrive.expect_tx per CTA of the pair (used in the leader only)
+      mbar_init(&empty[s], 1);     // the leader's commit, delivered to both CTAs
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);     // the leader's commit, delivered to both CTAs
+      mbar_init(&tempty[i], 8);    // four epilogue warps of each CTA (used in the leader only)
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    for (int i = 0; i <= RUN_LEVELS; ++i) tma_prefetch_desc(&am.m[i]);
+    tma_prefetch_desc(&tmBv0);
+    tma_prefetch_desc(&tmBv1);
+    tma_prefetch_desc(&tmBt0);
+    tma_prefetch_desc(&tmBt1);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();              // both CTAs' barriers exist before anybody signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int Mv = p.counts[0], Mt = p.counts[1], cap = p.counts[2];
+  const int tiles_v = (Mv + PAIR_BM - 1) / PAIR_BM;
+  const int m_tiles = tiles_v + (Mt + PAIR_BM - 1) / PAIR_BM;
+  constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const int n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_steps = (p.k_len + BK - 1) / BK;
+  const int text_base = text_row_base(Mv);
+
+  // this CTA's 128 rows of pair tile t
+  auto cta_tile = [&](int t) {
+    TileCoord c;
+    const int per_super = p.group_m * n_tiles;
+    const int st = t / per_super;
+    const int r = t - st * per_super;
+    const int m0 = st * p.group_m;
+    const int gm = min(p.group_m, m_tiles - m0);
+    c.nt = r / gm;
+    c.mt = m0 + (r - c.nt * gm);
+    c.text = c.mt >= tiles_v;
+    const int lt = c.text ? c.mt - tiles_v : c.mt;
+    c.row0 = lt * PAIR_BM + static_cast<int>(rank) * BM;
+    const int cnt = c.text ? Mt : Mv;
+    c.rows = max(0, min(BM, cnt - c.row0));
+    c.list_off = c.text ? cap : 0;
+    return c;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (both CTAs)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
+      const TileCoord tc = cta_tile(t);
+      int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
+      int run_lanes = 0;
+      if constexpr (A_MODE == A_GATHER) {
+        const int lr = 4 * lane;
+        const int valid = min(4, max(0, tc.rows - lr));
+        if (valid > 0) {
+          const int4 v = *reinterpret_cast<const int4*>(p.perm + tc.list_off + tc.row0 + lr);
+          r0 = v.x;
+          if (valid > 1) r1 = v.y;
+          if (valid > 2) r2 = v.z;
+          if (valid > 3) r3 = v.w;
+        }
+        run_lanes = run_block_lanes(lane, 32, r0, r1, r2, r3, valid, p.max_run_rows >> 2);
+      }
+      const bool run_lead = run_lanes > 0 && (lane & (run_lanes - 1)) == 0;
+      const CUtensorMap* run_map = &am.m[run_lanes > 0 ? 32 - __clz(run_lanes) : 0];
+      const bool empty_half = (A_MODE == A_GATHER) && tc.rows == 0;   // nothing to fetch: one out-of-range box
+      const CUtensorMap* mB = (EPI == EPI_SWIGLU) ? (tc.text ? (rank ? &tmBt1 : &tmBt0) : (rank ? &tmBv1 : &tmBv0))
+                                                  : (tc.text ? &tmBt0 : &tmBv0);
+      for (int ks = 0; ks < k_steps; ++ks) {
+        int w = 1;
+        if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
+        w = __shfl_sync(0xFFFFFFFFu, w, 0);
+        if (!w) {
+          if (lane == 0) report(p.status, ST_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        uint8_t* sa = smem + stage * PAIR_STAGE_BYTES;
+        uint8_t* sb = sa + A_BYTES;
+        const uint32_t lead_full = mapa_shared(smem_u32(&full[stage]), 0);
+        if (lane == 0) mbar_arrive_expect_tx_cluster(lead_full, PAIR_STAGE_BYTES);
+        __syncwarp();
+        const int kx = ks * BK;
+        if constexpr (A_MODE == A_GATHER) {
+          if (empty_half) {
+            if (lane == 0) tma_load_2d_pair(sa, &am.m[RUN_LEVELS], lead_full, kx, p.pad_row);
+          } else if (run_lanes == 0) {
+            tma_gather4_pair(sa + lane * 512, &am.m[0], lead_full, kx, r0, r1, r2, r3);
+          } else if (run_lead) {
+            tma_load_2d_pair(sa + lane * 512, run_map, lead_full, kx, r0);
+          }
+        } else {
+          if (lane == 0)
+            tma_load_2d_pair(sa, &am.m[RUN_LEVELS], lead_full, kx, (tc.text ? text_base : 0) + tc.row0);
+        }
+        if (lane == 0) {
+          // this CTA's half of the B tile
+          const int n0 = (EPI == EPI_SWIGLU) ? tc.nt * (BN / 2) : tc.nt * BN + static_cast<int>(rank) * (BN / 2);
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sb, mB, lead_full, kx, n0);
+          } else {
+            tma_load_2d_pair(sb, mB, lead_full, n0, kx);
+            tma_load_2d_pair(sb + PAIR_B_BYTES / 2, mB, lead_full, n0 + 64, kx);
+          }
+        }
+        if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(PAIR_BM, BN, false, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+          report(p.status, ST_TIMEOUT_MMA_TMEM);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            report(p.status, ST_TIMEOUT_MMA_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * PAIR_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = umma_smem_desc(a_addr + kk * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc(b_addr + kk * (UMMA_K * 128), PAIR_B_BYTES / 2, 1024)
+                                     : umma_smem_desc(b_addr + kk * (UMMA_K * 2), 16, 1024);
+            umma_bf16<2>(tmem_d, da, db, idesc, (ks | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage], 3);
+          if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tfull[acc], 3);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    int it = 0;
+    for (int t = pair_id; t < total_tiles; t += num_pairs, ++it) {
+      const TileCoord tc = cta_tile(t);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const bool valid = row < tc.rows;
+      int64_t dst_row = 0;
+      if (valid) {
+        if constexpr (OUT_MODE == OUT_SCATTER) dst_row = p.perm[tc.list_off + tc.row0 + row];
+        else dst_row = static_cast<int64_t>(tc.text ? text_base : 0) + tc.row0 + row;
+      }
+      int w = 1;
+      if (lane == 0) w = mbar_wait(&tfull[acc], acc_phase, abort_flag) ? 1 : 0;
+      w = __shfl_sync(0xFFFFFFFFu, w, 0);
+      if (!w) {
+        if (lane == 0) report(p.status, ST_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      epilogue_row<EPI>(taddr, p.out + dst_row * p.ldo, valid, tc.nt * N_PER_TILE, p.n_out);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the partner's shared memory and barriers stay alive until both CTAs are done
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<2>(tmem_base, TMEM_COLS);
   }
 }
 
@@ -710,14 +964,50 @@ static int pick_group_m(int64_t k_len) {
   return static_cast<int>(g);
 }
 
+// Tile table (replaces the reference's JSON lookup, ffn_kernel/utils.py:3-5): CTA pairs with
+// 256-row tiles once there are enough rows to fill them, single CTAs with 128-row tiles below.
+// FFNK_PAIR=0/1 overrides the choice for experiments.
+static bool use_pair_tiles(int64_t M) {
+  static const int forced = [] {
+    const char* e = getenv("FFNK_PAIR");
+    return e ? atoi(e) : -1;
+  }();
+  if (forced >= 0) return forced != 0;
+  return M >= 4096;
+}
+
 template <int A_MODE, int EPI, int OUT_MODE>
 static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn, const GemmParams& p,
-                       int64_t m_tiles_max, cudaStream_t stream) {
+                       int64_t M, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
   constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   const int64_t n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
-  int64_t grid = m_tiles_max * n_tiles;
+  if (use_pair_tiles(M)) {
+    int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
+    if (pairs > dev.sm_count / 2) pairs = dev.sm_count / 2;
+    if (pairs < 1) pairs = 1;
+    auto go = [&](auto kernel) -> int {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+      if (e != cudaSuccess) return cuda_status(e);
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+      cfg.blockDim = dim3(GEMM_THREADS);
+      cfg.dynamicSmemBytes = PAIR_SMEM;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      return cuda_status(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB[0], tmB[1], tmB[2], tmB[3], p));
+    };
+    return b_mn ? go(routed_gemm_pair_kernel<A_MODE, EPI, OUT_MODE, true>)
+                : go(routed_gemm_pair_kernel<A_MODE, EPI, OUT_MODE, false>);
+  }
+  int64_t grid = ((M + BM - 1) / BM + 1) * n_tiles;
   if (grid > dev.sm_count) grid = dev.sm_count;
   if (grid < 1) grid = 1;
   auto go = [&](auto kernel) -> int {
@@ -754,8 +1044,7 @@ extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(c), ldc, static_cast<int>(N), static_cast<int>(K),
                static_cast<int>(M), pick_group_m(K), max_run_rows(), status};
-  return launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1,
-                                                       static_cast<cudaStream_t>(stream));
+  return launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1,
@@ -778,10 +1067,9 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
   }
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(out), ldo, static_cast<int>(h), static_cast<int>(d),
                static_cast<int>(M), pick_group_m(d), max_run_rows(), status};
-  const int64_t mt = (M + BM - 1) / BM + 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return routed_out ? launch_gemm<A_GATHER, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, mt, s)
-                    : launch_gemm<A_GATHER, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, mt, s);
+  return routed_out ? launch_gemm<A_GATHER, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, M, s)
+                    : launch_gemm<A_GATHER, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, M, s);
 }
 
 extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
@@ -791,7 +1079,7 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   if (!inter || !w2 || !u2 || !perm || !counts || !y) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
   if ((ldi & 7) || (ldy & 7) || ldi < h || ldy < d || (reinterpret_cast<uintptr_t>(y) & 15)) return FFNK_ERR_ALIGN;
-  const int64_t rows = ffnk_route_capacity(M) + BM;
+  const int64_t rows = ffnk_route_capacity(M) + 512;
   AMaps tmA;
   CUtensorMap tmB[4];
   int r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], inter, h, rows, ldi, BK, BM);
@@ -804,8 +1092,7 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(y), ldy, static_cast<int>(d), static_cast<int>(h),
                static_cast<int>(M), pick_group_m(h), max_run_rows(), status};
-  return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1,
-                                                       static_cast<cudaStream_t>(stream));
+  return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
@@ -846,7 +1133,7 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     tmB[3] = tmB[2];
     GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(da), ldda, static_cast<int>(K), static_cast<int>(N),
                  static_cast<int>(M), pick_group_m(N), max_run_rows(), status};
-    r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, (M + BM - 1) / BM + 1, s);
+    r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, s);
     if (r) return r;
   }
   // dW: output in the weight's storage order; P supplies the storage rows, Q the storage columns

@@ -84,7 +84,7 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
             return y
         _phase("route")
         rt = _mask_route(mask, M, dev, rt)
-        inter = torch.empty((rt.cap + 128, h), device=dev, dtype=torch.bfloat16)
+        inter = torch.empty((rt.cap + 512, h), device=dev, dtype=torch.bfloat16)
         _phase("gateup")
         check("ffnk_ffn_gateup", L.ffnk_ffn_gateup(
             x.data_ptr(), x.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),

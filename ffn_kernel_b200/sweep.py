@@ -72,7 +72,7 @@ def main():
             check_status()
             return
         rt = route(c.mask)
-        inter = torch.empty((rt.cap + 128, h), device=dev, dtype=torch.bfloat16)
+        inter = torch.empty((rt.cap + 512, h), device=dev, dtype=torch.bfloat16)
         y = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
 
         def gateup():

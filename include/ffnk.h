@@ -111,8 +111,8 @@ int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, cons
  *     t1 = x @ (mask ? w1 : u1),  t3 = x @ (mask ? w3 : u3),  out = silu(t1) * t3
  * x [M,d]; w1,w3,u1,u3 [d,h] sharing one pair of strides; out bf16.
  *   routed_out == 0: out is [M, h] in token order (what the reference function returns).
- *   routed_out != 0: out is the routed intermediate [(cap + 128), h]: visual rows first,
- *                    text rows from row 128 * ceil(Mv / 128); rows in between are not written.
+ *   routed_out != 0: out is the routed intermediate [(cap + 512), h]: visual rows first,
+ *                    text rows from row 256 * ceil(Mv / 256); rows in between are not written.
  * ------------------------------------------------------------------------------------- */
 int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1, const void* u3,
                     int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* out,
@@ -124,7 +124,7 @@ int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const void* w3, 
  * MaskedFFN.forward (ffn_kernel/ops.py:28-32), whose second step is _bf16_linear_forward on
  * the intermediate:
  *     y[token, :] = inter[routed row of token, :] @ (mask[token] ? w2 : u2)
- * inter [(cap + 128), h] as written by ffnk_ffn_gateup; w2,u2 [h,d]; y [M,d] bf16.
+ * inter [(cap + 512), h] as written by ffnk_ffn_gateup; w2,u2 [h,d]; y [M,d] bf16.
  * ------------------------------------------------------------------------------------- */
 int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
                   int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy, int64_t M,
