@@ -43,9 +43,10 @@ def measured_peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             p = json.load(f)
-        return dict(tflops=float(p["bf16_tflops"]), hbm=float(p["hbm_gbs"]), source="measured")
+        return dict(tflops=float(p["bf16_tflops"]), tflops_sustained=float(p.get("bf16_tflops_sustained", 0)) or None,
+                    hbm=float(p["hbm_gbs"]), source="measured")
     except Exception:
-        return dict(tflops=1590.0, hbm=6650.0, source="fallback")
+        return dict(tflops=1590.0, tflops_sustained=1400.0, hbm=6650.0, source="fallback")
 
 
 class ClockSampler:
@@ -224,7 +225,7 @@ def run_ours(args):
 
     # gate/up launch durations from the events recorded on the launching stream
     names = [n for n, _ in phase_events]
-    gateup_ms, down_ms, route_ms = [], [], []
+    gateup_ms, down_ms, route_ms, permute_ms = [], [], [], []
     for i in range(len(phase_events) - 1):
         n, ev = phase_events[i]
         dt = ev.elapsed_time(phase_events[i + 1][1])
@@ -232,8 +233,10 @@ def run_ours(args):
             gateup_ms.append(dt)
         elif n == "down" and names[i + 1] == "end":
             down_ms.append(dt)
-        elif n == "route" and names[i + 1] == "gateup":
+        elif n == "route" and names[i + 1] in ("gateup", "permute"):
             route_ms.append(dt)
+        elif n == "permute" and names[i + 1] == "gateup":
+            permute_ms.append(dt)
     n_ffn_calls = len(gateup_ms)
     rows_per_call = M / max(1, (args.chunks if mode == "tp" else 1))
 
@@ -246,11 +249,14 @@ def run_ours(args):
     if gateup_ms:
         g_ms = statistics.mean(gateup_ms)
         achieved = 4.0 * rows_per_call * d * h_local / (g_ms * 1e-3) / 1e12
-        roofline = {"bound": "tensor", "kernel": "routed_gemm_kernel<gather, swiglu, routed> (gate/up)",
+        roofline = {"bound": "tensor", "kernel": "routed_gemm_kernel, gate/up GEMM with SwiGLU epilogue",
                     "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                     "peak_source": f"{peaks['source']} burst bf16 (MEASURED_PEAKS.json)",
+                    "peak_sustained": peaks["tflops_sustained"],
+                    "frac_of_sustained": achieved / peaks["tflops_sustained"] if peaks["tflops_sustained"] else None,
                     "launch_ms": g_ms, "down_launch_ms": statistics.mean(down_ms) if down_ms else None,
                     "route_launch_ms": statistics.mean(route_ms) if route_ms else None,
+                    "permute_launch_ms": statistics.mean(permute_ms) if permute_ms else None,
                     "traffic": args.traffic_bytes}
 
     # ---- end to end: activations and mask start in pinned host memory, result ends there -------
@@ -316,7 +322,7 @@ def run_ours(args):
                          "bf16, both branches dense then mask-selected as the reference module does"}
 
     if rank == 0:
-        kernels_per_call = 3      # routing scan, gate/up GEMM, down GEMM
+        kernels_per_call = 3 + (1 if permute_ms else 0)   # routing scan, (row permute,) gate/up GEMM, down GEMM
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,

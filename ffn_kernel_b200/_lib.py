@@ -26,8 +26,10 @@ SIGNATURES = {
     "ffnk_linear_bwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                 c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                 c_int64, c_void_p, c_void_p]),
+    "ffnk_permute_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                  c_void_p]),
     "ffnk_ffn_gateup": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
-                                c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int64,
+                                c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_int64, c_int64,
                                 c_void_p, c_void_p]),
     "ffnk_ffn_down": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
                               c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
@@ -37,6 +39,7 @@ SIGNATURES = {
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "ffnk_read_status": (c_int, [c_void_p, c_int, c_void_p]),
     "ffnk_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
+    "ffnk_debug_profile_buffer": (c_int, [c_void_p]),
     "ffnk_status_string": (c_char_p, [c_int]),
 }
 

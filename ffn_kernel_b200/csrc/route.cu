@@ -190,6 +190,69 @@ extern "C" int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* c
 }
 
 // -------------------------------------------------------------------------------------------
+// Row permutation into routed order: out[routed row of token t] = x[t].
+//
+// The GEMMs can gather token rows themselves (TMA boxes for runs of consecutive tokens, gather4
+// for ragged rows), but every row tile that straddles a run boundary then costs several TMA
+// instructions per k-step, and the TMA unit retires only about one instruction per 40 ns.  For
+// wide FFNs one extra pass over x (2 * M * d * 2 bytes of HBM traffic, a percent or two of the
+// GEMM time) is cheaper: afterwards every A tile is one tiled box whatever the mask looks like.
+// Routed layout as for the FFN intermediate: visual rows from row 0, text rows from row
+// 256 * ceil(Mv / 256).  HBM bound; algorithmic traffic 4 * d bytes per token.
+// -------------------------------------------------------------------------------------------
+namespace ffnk {
+constexpr int kPermuteThreads = 256;
+
+__global__ void __launch_bounds__(kPermuteThreads) permute_rows_kernel(const uint4* __restrict__ x, int64_t ldx16,
+                                                                       const int* __restrict__ perm,
+                                                                       const int* __restrict__ counts,
+                                                                       uint4* __restrict__ out, int64_t ldo16,
+                                                                       int chunks) {
+  const int Mv = counts[0], Mt = counts[1], cap = counts[2];
+  const int M = Mv + Mt;
+  const int text_base = ((Mv + 255) >> 8) << 8;
+  const int warps_per_block = kPermuteThreads / 32;
+  const int lane = threadIdx.x & 31;
+  for (int i = blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < M; i += gridDim.x * warps_per_block) {
+    const bool text = i >= Mv;
+    const int tok = text ? perm[cap + (i - Mv)] : perm[i];
+    const int64_t dst = text ? static_cast<int64_t>(text_base) + (i - Mv) : i;
+    const uint4* src_row = x + static_cast<int64_t>(tok) * ldx16;
+    uint4* dst_row = out + dst * ldo16;
+    for (int c = lane; c < chunks; c += 128) {
+      uint4 v0, v1, v2, v3;
+      const bool b1 = c + 32 < chunks, b2 = c + 64 < chunks, b3 = c + 96 < chunks;
+      v0 = __ldg(src_row + c);
+      if (b1) v1 = __ldg(src_row + c + 32);
+      if (b2) v2 = __ldg(src_row + c + 64);
+      if (b3) v3 = __ldg(src_row + c + 96);
+      dst_row[c] = v0;
+      if (b1) dst_row[c + 32] = v1;
+      if (b2) dst_row[c + 64] = v2;
+      if (b3) dst_row[c + 96] = v3;
+    }
+  }
+}
+}  // namespace ffnk
+
+extern "C" int ffnk_permute_rows(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out,
+                                 int64_t ldo, int64_t M, int64_t d, void* stream_) {
+  if (M == 0) return 0;
+  if (!x || !perm || !counts || !out) return FFNK_ERR_NULL;
+  if (M < 0 || M >= (1ll << 30) || d < 8 || (d & 7) || d >= (1ll << 30)) return FFNK_ERR_SHAPE;
+  if ((ldx & 7) || (ldo & 7) || ldx < d || ldo < d || (reinterpret_cast<uintptr_t>(x) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return FFNK_ERR_ALIGN;
+  const DeviceInfo& dev = device_info();
+  int64_t blocks = (M + 7) / 8;
+  const int64_t max_blocks = static_cast<int64_t>(dev.sm_count) * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  permute_rows_kernel<<<static_cast<unsigned>(blocks), kPermuteThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const uint4*>(x), ldx / 8, perm, counts, static_cast<uint4*>(out), ldo / 8, static_cast<int>(d / 8));
+  return cuda_status(cudaGetLastError());
+}
+
+// -------------------------------------------------------------------------------------------
 // Routing without any allocation by anybody.
 //
 // ffnk_route() needs a few kilobytes of scan state that the caller has to allocate.  Some hosts

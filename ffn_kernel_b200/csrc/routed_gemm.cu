@@ -55,6 +55,7 @@ struct GemmParams {
   int group_m;          // m-tiles per super-tile of the tile order
   int max_run_rows;     // largest tiled box used for runs of consecutive tokens (0: gather4 only)
   int* status;
+  long long* prof;      // optional per-CTA wait-cycle counters (8 per CTA), see ffnk_debug_profile_buffer
 };
 
 // Views of one row-gathered activation matrix: m[0] fetches single rows (gather4); m[1 + i]
@@ -508,6 +509,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    long long t_begin = clock64(), t_wait = 0;
     for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
       const TileCoord tc = cta_tile(t);
       int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
@@ -531,8 +533,10 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
                                                   : (tc.text ? &tmBt0 : &tmBv0);
       for (int ks = 0; ks < k_steps; ++ks) {
         int w = 1;
+        const long long tw = clock64();
         if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
         w = __shfl_sync(0xFFFFFFFFu, w, 0);
+        t_wait += clock64() - tw;
         if (!w) {
           if (lane == 0) report(p.status, ST_TIMEOUT_PRODUCER);
           ok = false;
@@ -569,6 +573,10 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
         if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1; }
       }
     }
+    if (p.prof && lane == 0) {
+      p.prof[blockIdx.x * 8 + 3] = t_wait;
+      p.prof[blockIdx.x * 8 + 4] = clock64() - t_begin;
+    }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader only)
     if (rank == 0 && lane == 0) {
@@ -577,21 +585,26 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      long long t_begin = clock64(), t_full = 0, t_tmem = 0;
       for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        long long tw = clock64();
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
           report(p.status, ST_TIMEOUT_MMA_TMEM);
           break;
         }
+        t_tmem += clock64() - tw;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int ks = 0; ks < k_steps; ++ks) {
+          tw = clock64();
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             report(p.status, ST_TIMEOUT_MMA_FULL);
             ok = false;
             break;
           }
+          t_full += clock64() - tw;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * PAIR_STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
@@ -607,6 +620,12 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
         }
         if (ok) umma_commit_pair(&tfull[acc], 3);
       }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = clock64() - t_begin;
+        p.prof[blockIdx.x * 8 + 1] = t_full;
+        p.prof[blockIdx.x * 8 + 2] = t_tmem;
+        p.prof[blockIdx.x * 8 + 7] = it;
+      }
     }
     __syncwarp();
   } else {
@@ -614,6 +633,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
     const int q = warp & 3;
     const int row = q * 32 + lane;
     int it = 0;
+    long long t_begin = clock64(), t_wait = 0;
     for (int t = pair_id; t < total_tiles; t += num_pairs, ++it) {
       const TileCoord tc = cta_tile(t);
       const int acc = it & 1;
@@ -625,8 +645,10 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
         else dst_row = static_cast<int64_t>(tc.text ? text_base : 0) + tc.row0 + row;
       }
       int w = 1;
+      const long long tw = clock64();
       if (lane == 0) w = mbar_wait(&tfull[acc], acc_phase, abort_flag) ? 1 : 0;
       w = __shfl_sync(0xFFFFFFFFu, w, 0);
+      t_wait += clock64() - tw;
       if (!w) {
         if (lane == 0) report(p.status, ST_TIMEOUT_EPILOGUE);
         break;
@@ -637,6 +659,10 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
+    }
+    if (p.prof && warp == 2 && lane == 0) {
+      p.prof[blockIdx.x * 8 + 5] = t_wait;
+      p.prof[blockIdx.x * 8 + 6] = clock64() - t_begin;
     }
   }
 
@@ -955,6 +981,8 @@ static int max_run_rows() {
   return v;
 }
 
+static long long* g_prof_buffer = nullptr;
+
 static int pick_group_m(int64_t k_len) {
   // keep one super-tile of A rows (group_m x 128 rows x K) near 32 MiB so that it stays in L2
   // while the weights stream past it
@@ -967,13 +995,15 @@ static int pick_group_m(int64_t k_len) {
 // Tile table (replaces the reference's JSON lookup, ffn_kernel/utils.py:3-5): CTA pairs with
 // 256-row tiles once there are enough rows to fill them, single CTAs with 128-row tiles below.
 // FFNK_PAIR=0/1 overrides the choice for experiments.
-static bool use_pair_tiles(int64_t M) {
+static bool use_pair_tiles(int64_t M, int a_mode, int epi) {
   static const int forced = [] {
     const char* e = getenv("FFNK_PAIR");
     return e ? atoi(e) : -1;
   }();
   if (forced >= 0) return forced != 0;
-  return M >= 4096;
+  // measured at d=4096/h=11008, M=16384: pairs gain ~4% when A arrives as one box per tile and the
+  // epilogue is a plain store (down projection), and lose ~3% under the two-weight SwiGLU tile
+  return M >= 4096 && a_mode == A_ROUTED && epi == EPI_STORE;
 }
 
 template <int A_MODE, int EPI, int OUT_MODE>
@@ -983,7 +1013,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
   constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   const int64_t n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
-  if (use_pair_tiles(M)) {
+  if (use_pair_tiles(M, A_MODE, EPI)) {
     int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
     if (pairs > dev.sm_count / 2) pairs = dev.sm_count / 2;
     if (pairs < 1) pairs = 1;
@@ -1043,21 +1073,28 @@ extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const
   tmB[1] = tmB[0];
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(c), ldc, static_cast<int>(N), static_cast<int>(K),
-               static_cast<int>(M), pick_group_m(K), max_run_rows(), status};
+               static_cast<int>(M), pick_group_m(K), max_run_rows(), status, g_prof_buffer};
   return launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1,
                                const void* u3, int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm,
-                               const int32_t* counts, void* out, int64_t ldo, int routed_out, int64_t M, int64_t d,
-                               int64_t h, int32_t* status, void* stream) {
+                               const int32_t* counts, void* out, int64_t ldo, int routed_in, int routed_out, int64_t M,
+                               int64_t d, int64_t h, int32_t* status, void* stream) {
   if (M == 0) return 0;
   if (!x || !w1 || !w3 || !u1 || !u3 || !perm || !counts || !out) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
   if ((ldx & 7) || (ldo & 7) || ldx < d || ldo < h || (reinterpret_cast<uintptr_t>(out) & 15)) return FFNK_ERR_ALIGN;
   AMaps tmA;
   CUtensorMap tmB[4];
-  int r = gather_maps(tmA, x, d, M, ldx);
+  int r;
+  if (routed_in) {
+    // x is [(cap + 512), d] in routed order (ffnk_permute_rows): one tiled box per A tile
+    r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], x, d, ffnk_route_capacity(M) + 512, ldx, BK, BM);
+    for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+  } else {
+    r = gather_maps(tmA, x, d, M, ldx);
+  }
   if (r) return r;
   bool mn = false, mn_i = false;
   const void* ws[4] = {w1, w3, u1, u3};
@@ -1066,8 +1103,11 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
     mn = mn_i;
   }
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(out), ldo, static_cast<int>(h), static_cast<int>(d),
-               static_cast<int>(M), pick_group_m(d), max_run_rows(), status};
+               static_cast<int>(M), pick_group_m(d), max_run_rows(), status, g_prof_buffer};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (routed_in)
+    return routed_out ? launch_gemm<A_ROUTED, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, M, s)
+                      : launch_gemm<A_ROUTED, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, M, s);
   return routed_out ? launch_gemm<A_GATHER, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, M, s)
                     : launch_gemm<A_GATHER, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, M, s);
 }
@@ -1091,7 +1131,7 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   tmB[1] = tmB[0];
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(y), ldy, static_cast<int>(d), static_cast<int>(h),
-               static_cast<int>(M), pick_group_m(h), max_run_rows(), status};
+               static_cast<int>(M), pick_group_m(h), max_run_rows(), status, g_prof_buffer};
   return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, static_cast<cudaStream_t>(stream));
 }
 
@@ -1132,7 +1172,7 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     tmB[1] = tmB[0];
     tmB[3] = tmB[2];
     GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(da), ldda, static_cast<int>(K), static_cast<int>(N),
-                 static_cast<int>(M), pick_group_m(N), max_run_rows(), status};
+                 static_cast<int>(M), pick_group_m(N), max_run_rows(), status, g_prof_buffer};
     r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, s);
     if (r) return r;
   }
@@ -1156,4 +1196,9 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
     return cuda_status(cudaGetLastError());
   }
+}
+
+extern "C" int ffnk_debug_profile_buffer(void* buffer) {
+  g_prof_buffer = static_cast<long long*>(buffer);
+  return 0;
 }

@@ -9,6 +9,8 @@ back to token order in its epilogue.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ._lib import check, lib
@@ -32,7 +34,7 @@ def _bf16_ffn_forward(x, w1, w3, u1, u3, mask, rt: Route | None = None):
         check("ffnk_ffn_gateup", lib().ffnk_ffn_gateup(
             x.data_ptr(), x.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),
             w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), out.data_ptr(), out.stride(0),
-            0, M, d, h, status_word(dev).data_ptr(), stream_ptr(dev)))
+            0, 0, M, d, h, status_word(dev).data_ptr(), stream_ptr(dev)))
     maybe_check(dev)
     return out
 
@@ -46,6 +48,19 @@ PHASE_HOOK = None
 def _phase(name: str) -> None:
     if PHASE_HOOK is not None:
         PHASE_HOOK(name)
+
+
+def permute_rows_first(M: int, d: int, h: int) -> bool:
+    """Tile-table entry for the FFN forward: copy x into routed order before the gate/up GEMM?
+
+    The copy moves 4*M*d bytes through HBM; the gate/up GEMM does 4*M*d*h FLOP.  With the GEMM
+    near 1.3 PFLOP/s and the copy near 5 TB/s the copy costs about 260/h of the GEMM time, while
+    gathering inside the GEMM costs 10-15 % on span masks and 3x on i.i.d. masks (row tiles that
+    straddle run boundaries need many TMA instructions per k-step).  FFNK_PERMUTE=0/1 overrides."""
+    forced = os.environ.get("FFNK_PERMUTE")
+    if forced is not None:
+        return forced != "0"
+    return M >= 2048 and h >= 2048
 
 
 def decode_max_tokens() -> int:
@@ -85,11 +100,19 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
         _phase("route")
         rt = _mask_route(mask, M, dev, rt)
         inter = torch.empty((rt.cap + 512, h), device=dev, dtype=torch.bfloat16)
+        routed_in = 0
+        if permute_rows_first(M, d, h):
+            _phase("permute")
+            xr = torch.empty((rt.cap + 512, d), device=dev, dtype=torch.bfloat16)
+            check("ffnk_permute_rows", L.ffnk_permute_rows(
+                x.data_ptr(), x.stride(0), rt.perm.data_ptr(), rt.counts.data_ptr(), xr.data_ptr(), xr.stride(0),
+                M, d, sp))
+            x, routed_in = xr, 1
         _phase("gateup")
         check("ffnk_ffn_gateup", L.ffnk_ffn_gateup(
             x.data_ptr(), x.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),
             w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), inter.stride(0),
-            1, M, d, h, st, sp))
+            routed_in, 1, M, d, h, st, sp))
         _phase("down")
         check("ffnk_ffn_down", L.ffnk_ffn_down(
             inter.data_ptr(), inter.stride(0), w2.data_ptr(), u2.data_ptr(), w2.stride(0), w2.stride(1),

@@ -77,14 +77,27 @@ def main():
 
         def gateup():
             L.ffnk_ffn_gateup(c.x.data_ptr(), d, c.w1.data_ptr(), c.w3.data_ptr(), c.u1.data_ptr(), c.u3.data_ptr(),
-                              1, d, rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), h, 1, M, d, h, st, sp)
+                              1, d, rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), h, 0, 1, M, d, h, st, sp)
 
         def down():
             L.ffnk_ffn_down(inter.data_ptr(), h, c.w2.data_ptr(), c.u2.data_ptr(), 1, h, rt.perm.data_ptr(),
                             rt.counts.data_ptr(), y.data_ptr(), d, M, d, h, st, sp)
 
+        xr = torch.empty((rt.cap + 512, d), device=dev, dtype=torch.bfloat16)
+
+        def permute():
+            L.ffnk_permute_rows(c.x.data_ptr(), d, rt.perm.data_ptr(), rt.counts.data_ptr(), xr.data_ptr(), d, M, d, sp)
+
+        def gateup_routed():
+            L.ffnk_ffn_gateup(xr.data_ptr(), d, c.w1.data_ptr(), c.w3.data_ptr(), c.u1.data_ptr(), c.u3.data_ptr(),
+                              1, d, rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), h, 1, 1, M, d, h, st, sp)
+
         t = timeit(gateup, a.iters, a.warmup)
-        emit(kernel="ffn_gateup", M=M, d=d, h=h, mask=a.mask, ms=t, tflops=4 * M * d * h / t / 1e9)
+        emit(kernel="ffn_gateup(gather in kernel)", M=M, d=d, h=h, mask=a.mask, ms=t, tflops=4 * M * d * h / t / 1e9)
+        t = timeit(permute, a.iters, a.warmup)
+        emit(kernel="permute_rows", M=M, d=d, mask=a.mask, ms=t, gbs=4 * M * d / t / 1e6)
+        t = timeit(gateup_routed, a.iters, a.warmup)
+        emit(kernel="ffn_gateup(routed input)", M=M, d=d, h=h, mask=a.mask, ms=t, tflops=4 * M * d * h / t / 1e9)
         t = timeit(down, a.iters, a.warmup)
         emit(kernel="ffn_down", M=M, d=d, h=h, mask=a.mask, ms=t, tflops=2 * M * d * h / t / 1e9)
         t = timeit(lambda: _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False), a.iters, a.warmup)

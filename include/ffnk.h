@@ -106,17 +106,29 @@ int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, cons
                     void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Copies the rows of x [M, d] into routed order: out [(cap + 512), d], visual rows first, text
+ * rows from row 256 * ceil(Mv / 256).  No counterpart in the reference (it never reorders
+ * tokens); used in front of ffnk_ffn_gateup(routed_in = 1) when one extra pass over x is
+ * cheaper than gathering ragged rows inside the GEMM.
+ * ------------------------------------------------------------------------------------- */
+int ffnk_permute_rows(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out, int64_t ldo,
+                      int64_t M, int64_t d, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * MaskedFFN gate/up projection with the SwiGLU epilogue.  Replaces _bf16_ffn_forward
  * (ffn_kernel/ffn.py:527-560) and _masked_ffn_infer (ffn_kernel/ffn.py:15-113):
  *     t1 = x @ (mask ? w1 : u1),  t3 = x @ (mask ? w3 : u3),  out = silu(t1) * t3
  * x [M,d]; w1,w3,u1,u3 [d,h] sharing one pair of strides; out bf16.
+ *   routed_in  == 0: x is [M, d] in token order; its rows are gathered by the kernel.
+ *   routed_in  != 0: x is [(cap + 512), d] already in routed order (ffnk_permute_rows).
  *   routed_out == 0: out is [M, h] in token order (what the reference function returns).
  *   routed_out != 0: out is the routed intermediate [(cap + 512), h]: visual rows first,
  *                    text rows from row 256 * ceil(Mv / 256); rows in between are not written.
  * ------------------------------------------------------------------------------------- */
 int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1, const void* u3,
                     int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* out,
-                    int64_t ldo, int routed_out, int64_t M, int64_t d, int64_t h, int32_t* status, void* stream);
+                    int64_t ldo, int routed_in, int routed_out, int64_t M, int64_t d, int64_t h, int32_t* status,
+                    void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * MaskedFFN down projection from the routed intermediate, rows scattered back to token order
@@ -149,6 +161,13 @@ int ffnk_read_status(int32_t* status, int clear, void* stream);
  * with a budget of `budget_us` microseconds, then records its status and exits normally.
  * Used by the tests to show that an expired wait surfaces as a status code. */
 int ffnk_selftest_bounded_wait(int32_t* status, int64_t budget_us, void* stream);
+
+/* Diagnostics: when `buffer` (device memory, 8 int64 per CTA of the largest grid, i.e. 8 * SM count)
+ * is non-null, the CTA-pair GEMM kernels launched afterwards store per-CTA cycle counters in it:
+ * [0] MMA-issuer total, [1] its wait for operands, [2] its wait for a free accumulator,
+ * [3] producer wait for a free stage, [4] producer total, [5] epilogue wait for an accumulator,
+ * [6] epilogue total, [7] tiles.  Pass null to switch it off (the default).  Process-wide. */
+int ffnk_debug_profile_buffer(void* buffer);
 
 /* Human-readable name of a return code or device status code (static storage). */
 const char* ffnk_status_string(int code);
