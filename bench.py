@@ -12,9 +12,12 @@ TFLOP/s (6*M*d*h per step: each token times its own modality's weights only) wit
 in HBM; ``e2e`` is the same metric with the step's activations and mask starting in pinned host
 memory and the result ending there.  Rank 0 prints one JSON line.
 
-N > 1 runs the tensor-parallel mode by default (weights sharded over h, partial outputs summed by
-NCCL all-reduce, total work fixed: strong scaling); ``--mode dp`` runs token-sharded data
-parallel (every rank its own batch, no communication: weak scaling).
+N > 1 shards the tokens by default (``--mode dp``: every rank routes and multiplies its own batch
+with replicated weights, no data-path collective, weak scaling) -- the tokens are independent
+units, so this is how the path partitions.  The same run then also times the tensor-parallel
+mode (weights sharded over h, partial outputs summed by NCCL all-reduce in token chunks, total
+work fixed) and reports it under ``"tp"``; ``--mode tp`` makes that the headline instead
+(strong scaling).
 """
 from __future__ import annotations
 
@@ -37,6 +40,9 @@ WORKLOADS = {
     "c2_ffn_d1024_h2048_m32768": dict(M=32768, d=1024, h=2048),
 }
 METRIC = "routed_bf16_tflops_maskedffn_fwd"
+# DRAM bytes per launch of the gate/up GEMM (dram__bytes_read.sum + dram__bytes_write.sum) from the
+# one-pass ncu capture summarised in profiles/bench_c4_launch_list.md
+GATEUP_DRAM_BYTES = {"c4_ffn_d4096_h11008_m16384": 1.60e9}
 
 
 def measured_peaks():
@@ -152,7 +158,7 @@ def run_ours(args):
     import torch.distributed as dist
     from ffn_kernel_b200 import MaskedFFN, check_status, tp
     from ffn_kernel_b200 import ffn as ffn_mod
-    from ffn_kernel_b200.synth import ffn_case
+    from ffn_kernel_b200.synth import ffn_case, ffn_tokens
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -167,8 +173,9 @@ def run_ours(args):
     wl = WORKLOADS[args.workload]
     M, d, h = wl["M"], wl["d"], wl["h"]
     mode = "single" if world == 1 else args.mode
-    seed = rank if mode == "dp" else 0          # dp: every rank has its own batch
-    case_cpu = ffn_case(M, d, h, seed=seed)
+    case_cpu = ffn_case(M, d, h, seed=0)        # weights are replicated (dp) or sharded views of these (tp)
+    if mode == "dp" and rank > 0:               # dp: every rank has its own batch of tokens
+        case_cpu.x, case_cpu.mask = ffn_tokens(M, d, seed=rank)
     case = case_cpu.to(dev)
     full_args = case.apply_args()
     if mode == "tp":
@@ -257,7 +264,9 @@ def run_ours(args):
                     "launch_ms": g_ms, "down_launch_ms": statistics.mean(down_ms) if down_ms else None,
                     "route_launch_ms": statistics.mean(route_ms) if route_ms else None,
                     "permute_launch_ms": statistics.mean(permute_ms) if permute_ms else None,
-                    "traffic": args.traffic_bytes}
+                    "traffic": args.traffic_bytes if args.traffic_bytes is not None
+                    else (GATEUP_DRAM_BYTES.get(args.workload) if mode != "tp" else None),
+                    "algorithmic_bytes": 2.0 * (rows_per_call * d + 2 * d * h_local * 2 + rows_per_call * h_local)}
 
     # ---- end to end: activations and mask start in pinned host memory, result ends there -------
     e2e = None
@@ -312,6 +321,35 @@ def run_ours(args):
                "tokens_per_s": M * (world if mode == "dp" else 1) * args.steps / e2e_s,
                "pipeline": "H2D of step i+1, compute of step i and D2H of step i-1 overlap on three streams"}
 
+    # ---- tensor-parallel timing alongside a token-sharded run ------------------------------------
+    tp_line = None
+    if world > 1 and mode == "dp" and not args.skip_tp:
+        x_tp, m_tp = x.clone(), mask.clone()
+        dist.broadcast(x_tp, 0)
+        m8 = m_tp.to(torch.uint8)
+        dist.broadcast(m8, 0)
+        m_tp = m8.bool()
+        w_tp = tp.shard_ffn_weights(*full_args[1:7], rank, world)      # views of the replicated weights
+        tp_steps = max(3, min(args.steps, 10))
+        for _ in range(3):
+            tp.masked_ffn_tp(x_tp, *w_tp, m_tp, chunks=args.chunks)
+        barrier()
+        t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0e.record()
+        for _ in range(tp_steps):
+            tp.masked_ffn_tp(x_tp, *w_tp, m_tp, chunks=args.chunks)
+        t1e.record()
+        barrier()
+        t = torch.tensor([t0e.elapsed_time(t1e)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        tp_ms = float(t.item()) / tp_steps
+        check_status()
+        tp_line = {"value": 6.0 * M * d * h / (tp_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": tp_ms,
+                   "steps": tp_steps, "scaling": "strong", "chunks": args.chunks,
+                   "collective": "NCCL all-reduce of the partial outputs, one per token chunk",
+                   "tokens_per_s": M / (tp_ms * 1e-3)}
+        del w_tp, x_tp
+
     # ---- CPU baseline (rank 0, single GPU only) -------------------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
@@ -335,7 +373,7 @@ def run_ours(args):
                        if args.workload.startswith("c4") else "inputs larger than L2"},
             "tokens_per_s": tokens_per_s,
             "frac_of_measured_bf16_peak": value / peaks["tflops"] / world,
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "tp": tp_line,
             "gpu_launches": kernels_per_call * max(1, n_ffn_calls),
         }
         print(json.dumps(line), flush=True)
@@ -350,8 +388,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c4_ffn_d4096_h11008_m16384")
-    ap.add_argument("--mode", choices=["tp", "dp"], default="tp", help="multi-GPU mode (N > 1)")
-    ap.add_argument("--chunks", type=int, default=4, help="token chunks per step in tp mode (overlap)")
+    ap.add_argument("--mode", choices=["tp", "dp"], default="dp", help="multi-GPU mode (N > 1)")
+    ap.add_argument("--skip-tp", action="store_true", help="do not add the tensor-parallel timing to a dp run")
+    ap.add_argument("--chunks", type=int, default=1,
+                    help="token chunks per step in tp mode (>1 overlaps all-reduce with GEMMs; measured slower)")
     ap.add_argument("--cpu-sample-rows", type=int, default=1024)
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")

@@ -39,6 +39,7 @@ SIGNATURES = {
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "ffnk_read_status": (c_int, [c_void_p, c_int, c_void_p]),
     "ffnk_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
+    "ffnk_set_sm_margin": (c_int, [c_int]),
     "ffnk_debug_profile_buffer": (c_int, [c_void_p]),
     "ffnk_status_string": (c_char_p, [c_int]),
 }

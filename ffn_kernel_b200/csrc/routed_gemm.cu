@@ -982,8 +982,19 @@ static int max_run_rows() {
 }
 
 static long long* g_prof_buffer = nullptr;
+static int g_sm_margin = 0;   // SMs the persistent GEMM grids leave free (for a concurrent collective)
+
+static int usable_sms(const DeviceInfo& dev) {
+  int n = dev.sm_count - g_sm_margin;
+  return n < 2 ? 2 : n;
+}
 
 static int pick_group_m(int64_t k_len) {
+  static const int forced = [] {
+    const char* e = getenv("FFNK_GROUP_M");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced > 0) return forced;
   // keep one super-tile of A rows (group_m x 128 rows x K) near 32 MiB so that it stays in L2
   // while the weights stream past it
   int64_t g = (32ll << 20) / (BM * k_len * 2);
@@ -1015,7 +1026,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   const int64_t n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
   if (use_pair_tiles(M, A_MODE, EPI)) {
     int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
-    if (pairs > dev.sm_count / 2) pairs = dev.sm_count / 2;
+    if (pairs > usable_sms(dev) / 2) pairs = usable_sms(dev) / 2;
     if (pairs < 1) pairs = 1;
     auto go = [&](auto kernel) -> int {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
@@ -1038,7 +1049,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
                 : go(routed_gemm_pair_kernel<A_MODE, EPI, OUT_MODE, false>);
   }
   int64_t grid = ((M + BM - 1) / BM + 1) * n_tiles;
-  if (grid > dev.sm_count) grid = dev.sm_count;
+  if (grid > usable_sms(dev)) grid = usable_sms(dev);
   if (grid < 1) grid = 1;
   auto go = [&](auto kernel) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
@@ -1190,7 +1201,7 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
                    k_major ? b_stride_n : b_stride_k, static_cast<int>(p_dim), static_cast<int>(q_dim),
                    static_cast<int>(M), max_run_rows() < 64 ? max_run_rows() : 64, status};
     int64_t grid = 2 * ((p_dim + BM - 1) / BM) * ((q_dim + BN - 1) / BN);
-    if (grid > dev.sm_count) grid = dev.sm_count;
+    if (grid > usable_sms(dev)) grid = usable_sms(dev);
     cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return cuda_status(e);
     wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
@@ -1200,5 +1211,11 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
 
 extern "C" int ffnk_debug_profile_buffer(void* buffer) {
   g_prof_buffer = static_cast<long long*>(buffer);
+  return 0;
+}
+
+extern "C" int ffnk_set_sm_margin(int sms) {
+  if (sms < 0 || sms > 128) return FFNK_ERR_SHAPE;
+  g_sm_margin = sms;
   return 0;
 }

@@ -4,6 +4,8 @@
     python -m ffn_kernel_b200.sweep linear   --M 32768 --K 4096 --N 4096 [--mask span] [--bwd]
     python -m ffn_kernel_b200.sweep route    --M 67108864
     python -m ffn_kernel_b200.sweep decode   --M 8 --d 1024 --h 2816 [--mask alternating]
+    FFNK_PAIR=1 python -m ffn_kernel_b200.sweep waits --M 16384 --d 4096 --h 11008
+        (wait-cycle counters of the CTA-pair GEMM kernels: who waits for whom, and the SM clock)
 
 Each kernel is launched through the C ABI and timed with CUDA events on the launching stream
 (warm-up first, inputs larger than L2 or rotated over several copies).  One JSON line per kernel.
@@ -47,7 +49,7 @@ def emit(**kw):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["ffn", "linear", "route", "decode", "once"])
+    ap.add_argument("what", choices=["ffn", "linear", "route", "decode", "once", "waits"])
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--d", type=int, default=4096)
     ap.add_argument("--h", type=int, default=11008)
@@ -61,6 +63,45 @@ def main():
     dev = torch.device("cuda", torch.cuda.current_device())
     L = lib()
     st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
+
+    if a.what == "waits":
+        M, d, h = a.M, a.d, a.h
+        c = ffn_case(M, d, h, seed=0, mask=edge_mask(M, a.mask, 0)).to(dev)
+        rt = route(c.mask)
+        inter = torch.empty((rt.cap + 512, h), device=dev, dtype=torch.bfloat16)
+        y = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        prof = torch.zeros(sms * 8, dtype=torch.int64, device=dev)
+        launches = {
+            "ffn_gateup(gather in kernel)": lambda: L.ffnk_ffn_gateup(
+                c.x.data_ptr(), d, c.w1.data_ptr(), c.w3.data_ptr(), c.u1.data_ptr(), c.u3.data_ptr(), 1, d,
+                rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), h, 0, 1, M, d, h, st, sp),
+            "ffn_down": lambda: L.ffnk_ffn_down(
+                inter.data_ptr(), h, c.w2.data_ptr(), c.u2.data_ptr(), 1, h, rt.perm.data_ptr(), rt.counts.data_ptr(),
+                y.data_ptr(), d, M, d, h, st, sp),
+        }
+        for name, fn in launches.items():
+            for _ in range(a.warmup):
+                fn()
+            torch.cuda.synchronize()
+            prof.zero_()
+            L.ffnk_debug_profile_buffer(prof.data_ptr())
+            ms = timeit(fn, 1, 0)
+            L.ffnk_debug_profile_buffer(None)
+            p = prof.view(sms, 8).cpu().double()
+            lead = p[0::2]
+            if float(lead[:, 0].sum()) == 0:
+                emit(kernel=name, note="no counters: this launch did not use the CTA-pair kernel (set FFNK_PAIR=1)")
+                continue
+            tot = float(lead[:, 0].mean())
+            emit(kernel=name, M=M, d=d, h=h, mask=a.mask, ms=ms, mma_cycles=tot, sm_mhz=tot / ms / 1e3,
+                 mma_wait_operands_pct=100 * float(lead[:, 1].mean()) / tot,
+                 mma_wait_accumulator_pct=100 * float(lead[:, 2].mean()) / tot,
+                 producer_wait_stage_pct=100 * float(p[:, 3].mean() / p[:, 4].mean()),
+                 epilogue_wait_accumulator_pct=100 * float(p[:, 5].mean() / p[:, 6].mean()),
+                 tiles_per_pair=float(lead[:, 7].mean()))
+        check_status()
+        return
 
     if a.what in ("ffn", "once"):
         M, d, h = a.M, a.d, a.h

@@ -114,6 +114,12 @@ def ffn_case(M: int, d: int, h: int, seed: int = 0, mask: torch.Tensor | None = 
     return FFNCase(x, *ws, mask)
 
 
+def ffn_tokens(M: int, d: int, seed: int, visual_frac: float = 0.5):
+    """One more batch of activations and mask for an existing FFN case (same weights, new tokens)."""
+    gen = torch.Generator().manual_seed(1000003 + seed)
+    return _randn_bf16((M, d), 1.0, gen), span_mask(M, 1000003 + seed, visual_frac=visual_frac)
+
+
 # The named benchmark configurations: name -> (kind, dims)
 CONFIGS = {
     "c1_linear_d1024_m4096": dict(op="linear", M=4096, K=1024, N=1024, visual_frac=0.5),

@@ -8,8 +8,10 @@ modes are additions around the unchanged operator API:
 * tensor parallel over the intermediate dimension ``h`` -- rank ``r`` holds columns
   ``[r*h/P, (r+1)*h/P)`` of the gate/up weights and the matching rows of the down weights as
   *views* of the full weights (no copies), computes a partial ``y`` with the ordinary
-  ``MaskedFFN.apply`` and the partials are summed by one all-reduce per token chunk.  With more
-  than one chunk the all-reduce of chunk ``i`` overlaps the GEMMs of chunk ``i+1``.
+  ``MaskedFFN.apply`` and the partials are summed by one all-reduce per token chunk (or one
+  reduce-scatter, leaving every rank with its block of rows).  With more than one chunk the
+  collective of chunk ``i`` overlaps the GEMMs of chunk ``i+1``; on 2 and 8 B200s one chunk was
+  fastest (the chunked GEMMs lose more than the overlap gains).
 """
 from __future__ import annotations
 
@@ -46,29 +48,62 @@ def shard_ffn_weights(w1, w2, w3, u1, u2, u3, rank: int, world: int):
 
 
 def masked_ffn_tp(x, w1, w2, w3, u1, u2, u3, mask, group=None, chunks: int = 1,
-                  ffn_fn: Callable | None = None, reduce_dtype: torch.dtype | None = None):
+                  ffn_fn: Callable | None = None, reduce_dtype: torch.dtype | None = None, sm_margin: int = 16):
     """Tensor-parallel MaskedFFN forward.  The weights are this rank's shards (see
     ``shard_ffn_weights``); ``x`` and ``mask`` are replicated.  Returns the full ``y`` on every rank.
 
     ``chunks`` splits the tokens into that many row blocks, each reduced as soon as it is
-    computed.  ``ffn_fn`` defaults to ``MaskedFFN.apply``; tests on CPU ranks pass a stand-in."""
+    computed.  While chunks are in flight the persistent GEMM grids leave ``sm_margin`` SMs free so
+    that the collective's kernels can run beside them instead of queueing behind them.
+    ``ffn_fn`` defaults to ``MaskedFFN.apply``; tests on CPU ranks pass a stand-in."""
+    set_margin = None
     if ffn_fn is None:
+        from ._lib import lib
         from .ops import MaskedFFN
         ffn_fn = MaskedFFN.apply
+        set_margin = lib().ffnk_set_sm_margin
     M = x.shape[0]
     chunks = max(1, min(chunks, max(1, M)))
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     bounds = [row_shard(M, c, chunks) for c in range(chunks)]
     y = torch.empty((M, w2.shape[1]), dtype=reduce_dtype or x.dtype, device=x.device)
     works = []
-    for b in bounds:
-        part = ffn_fn(x[b], w1, w2, w3, u1, u2, u3, mask[b])
-        y[b] = part                              # cast to the reduction dtype if one was asked for
-        if world > 1:
-            works.append(dist.all_reduce(y[b], op=dist.ReduceOp.SUM, group=group, async_op=True))
+    overlap = set_margin is not None and world > 1 and chunks > 1 and sm_margin > 0
+    if overlap:
+        set_margin(sm_margin)
+    try:
+        for b in bounds:
+            part = ffn_fn(x[b], w1, w2, w3, u1, u2, u3, mask[b])
+            y[b] = part                              # cast to the reduction dtype if one was asked for
+            if world > 1:
+                works.append(dist.all_reduce(y[b], op=dist.ReduceOp.SUM, group=group, async_op=True))
+    finally:
+        if overlap:
+            set_margin(0)
     for w in works:
         w.wait()
     return y if y.dtype == x.dtype else y.to(x.dtype)
+
+
+def masked_ffn_tp_reduce_scatter(x, w1, w2, w3, u1, u2, u3, mask, group=None, ffn_fn: Callable | None = None):
+    """Tensor-parallel MaskedFFN forward that leaves the output row-sharded: rank ``r`` returns
+    ``(rows, y[rows])`` with ``rows = row_shard(M, r, world)``.  Half the traffic of the all-reduce;
+    for callers whose next operator is token-parallel.  ``M`` must be a multiple of the world size."""
+    if ffn_fn is None:
+        from .ops import MaskedFFN
+        ffn_fn = MaskedFFN.apply
+    M = x.shape[0]
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if M % world:
+        raise ValueError(f"M = {M} must be a multiple of the world size {world} for reduce-scatter")
+    part = ffn_fn(x, w1, w2, w3, u1, u2, u3, mask)
+    rows = row_shard(M, rank, world)
+    if world == 1:
+        return rows, part
+    out = torch.empty((M // world, part.shape[1]), dtype=part.dtype, device=part.device)
+    dist.reduce_scatter_tensor(out, part.contiguous(), op=dist.ReduceOp.SUM, group=group)
+    return rows, out
 
 
 def masked_linear_dp(a, b1, b2, mask, rank: int, world: int, linear_fn: Callable | None = None):

@@ -162,6 +162,11 @@ int ffnk_read_status(int32_t* status, int clear, void* stream);
  * Used by the tests to show that an expired wait surfaces as a status code. */
 int ffnk_selftest_bounded_wait(int32_t* status, int64_t budget_us, void* stream);
 
+/* The GEMM kernels are persistent and by default occupy every SM.  A caller that overlaps them
+ * with a collective on another stream (tensor-parallel chunks) sets a margin so that many SMs stay
+ * free for the collective's kernels; 0 restores the default.  Process-wide, affects later launches. */
+int ffnk_set_sm_margin(int sms);
+
 /* Diagnostics: when `buffer` (device memory, 8 int64 per CTA of the largest grid, i.e. 8 * SM count)
  * is non-null, the CTA-pair GEMM kernels launched afterwards store per-CTA cycle counters in it:
  * [0] MMA-issuer total, [1] its wait for operands, [2] its wait for a free accumulator,

@@ -41,8 +41,14 @@ def _worker(rank, world, port, chunks, out):
         err_dp = O.max_rel_err(part, full[rows])
         counts = [None] * world
         dist.all_gather_object(counts, (rows.start, rows.stop))
+        # a world-size mismatch in the row count is refused before any collective
+        try:
+            tp.masked_ffn_tp_reduce_scatter(c.x[:299], *shards, c.mask[:299], ffn_fn=_oracle_ffn)
+            refused = False
+        except ValueError:
+            refused = True
         if rank == 0:
-            out.put((err_tp, err_dp, counts))
+            out.put((err_tp, err_dp, counts, refused))
     finally:
         dist.destroy_process_group()
 
@@ -58,7 +64,8 @@ def test_tp_and_dp_two_ranks(chunks):
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
-    err_tp, err_dp, counts = q.get()
+    err_tp, err_dp, counts, refused = q.get()
+    assert refused
     assert err_tp < 5e-3 and err_dp < 1e-6          # y is returned in bf16 (one rounding)
     assert counts == [(0, 151), (151, 301)]          # contiguous, disjoint, covering
 
