@@ -37,6 +37,11 @@ SIGNATURES = {
     "ffnk_ffn_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ffnk_ffn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
+    "ffnk_ffn_permute_first": (c_int, [c_int64, c_int64, c_int64]),
+    "ffnk_ffn_forward": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
+                                 c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "ffnk_read_status": (c_int, [c_void_p, c_int, c_void_p]),
     "ffnk_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
     "ffnk_set_sm_margin": (c_int, [c_int]),

@@ -9,8 +9,9 @@
 //     accumulate).  The k-slots of the instruction are assigned so that one 16-byte chunk of a
 //     weight row and the same 16-byte chunk of a token row feed two MMAs directly from
 //     registers, with no shuffles: lane (g, t) of the warp holds chunk t of rows g and g+8;
-//   * the contraction is split over the warps of a CTA and summed through shared memory, which
-//     puts enough loads in flight per SM to cover HBM latency.
+//   * the contraction is split over the warps of a CTA (8 for gate/up, 16 for down) and summed
+//     through shared memory; at d = 1024 / h = 2816 every lane issues all of its weight loads
+//     in one batch, so a CTA pays HBM latency once.
 // The two phases (gate/up with the SiLU(t1)*t3 epilogue, then the down projection) are two
 // launches chained with programmatic dependent launch: the second kernel's CTAs start early,
 // pull their first weights, and wait for the first kernel only before they read the
@@ -62,7 +63,7 @@ struct DecodeParams {
 
 // GATEUP: out[tok, r] = silu(x[tok] . wa[r]) * (x[tok] . wb[r]);  otherwise out[tok, r] = x[tok] . wa[r]
 // WAIT_PRIMARY: this launch depends on the previous kernel in the stream for `x`.
-template <bool GATEUP, bool WAIT_PRIMARY, int WARPS>
+template <bool GATEUP, bool WAIT_PRIMARY, int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32) decode_phase_kernel(const DecodeParams p) {
   __shared__ float red[WARPS][32][GATEUP ? 8 : 4];
   __shared__ int s_tok[kDecodeMaxTokens];
@@ -73,11 +74,12 @@ __global__ void __launch_bounds__(WARPS * 32) decode_phase_kernel(const DecodePa
   const int g = lane >> 2, t = lane & 3;
   if constexpr (!WAIT_PRIMARY) pdl_launch_dependents();
 
-  if (threadIdx.x == 0) {
-    int n = 0;
-    for (int m = 0; m < p.M; ++m)
-      if ((p.mask[m] != 0) == (modality == 0)) s_tok[n++] = m;
-    s_ntok = n;
+  if (warp == 0) {
+    // one mask byte per lane, all loads in flight together; the modality's tokens keep their order
+    const bool mine = lane < p.M && ((p.mask[lane] != 0) == (modality == 0));
+    const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, mine);
+    if (mine) s_tok[__popc(ballot & ((1u << lane) - 1u))] = lane;
+    if (lane == 0) s_ntok = __popc(ballot);
   }
   __syncthreads();
   const int ntok = s_ntok;
@@ -98,7 +100,6 @@ __global__ void __launch_bounds__(WARPS * 32) decode_phase_kernel(const DecodePa
   const uint4 zero = make_uint4(0, 0, 0, 0);
   const int kblocks = (p.K + 31) / 32;      // 32 contraction elements per step: 4 lanes x 16 bytes per row
 
-  constexpr int UNROLL = 4;
   bool waited = !WAIT_PRIMARY;
   for (int kb0 = warp; kb0 < kblocks; kb0 += WARPS * UNROLL) {
     uint4 a_lo[UNROLL], a_hi[UNROLL], b_lo[UNROLL], b_hi[UNROLL], xv[UNROLL];
@@ -222,8 +223,8 @@ extern "C" int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const
   p1.M = static_cast<int>(M);
   p1.K = static_cast<int>(d);
   p1.rows = static_cast<int>(h);
-  cudaError_t e = launch_phase(decode_phase_kernel<true, false, 4>,
-                               dim3(static_cast<unsigned>((h + kDecodeRows - 1) / kDecodeRows), 2), 4 * 32, false,
+  cudaError_t e = launch_phase(decode_phase_kernel<true, false, 8, 4>,
+                               dim3(static_cast<unsigned>((h + kDecodeRows - 1) / kDecodeRows), 2), 8 * 32, false,
                                stream, p1);
   if (e != cudaSuccess) return cuda_status(e);
 
@@ -240,7 +241,7 @@ extern "C" int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const
   p2.M = static_cast<int>(M);
   p2.K = static_cast<int>(h);
   p2.rows = static_cast<int>(d);
-  e = launch_phase(decode_phase_kernel<false, true, 8>,
-                   dim3(static_cast<unsigned>((d + kDecodeRows - 1) / kDecodeRows), 2), 8 * 32, true, stream, p2);
+  e = launch_phase(decode_phase_kernel<false, true, 16, 6>,
+                   dim3(static_cast<unsigned>((d + kDecodeRows - 1) / kDecodeRows), 2), 16 * 32, true, stream, p2);
   return cuda_status(e);
 }

@@ -1,0 +1,97 @@
+// The whole MaskedFFN forward behind one C call: routing scan, optional row permutation, gate/up
+// GEMM with the SwiGLU epilogue, down projection with the scatter epilogue -- or the
+// weight-streaming decode pair for a handful of tokens.  Same contract as MaskedFFN.forward
+// (ffn_kernel/ops.py:28-32).  One call keeps the host cost of a forward pass at a few
+// microseconds, which is what matters when the kernels themselves take ten.
+#include <cstdlib>
+
+#include "ffnk_internal.h"
+
+namespace ffnk {
+
+static int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
+
+// Tile-table entry: copy x into routed order before the gate/up GEMM?  The copy moves 4*M*d bytes
+// through HBM (measured 5.6-5.9 TB/s); gathering inside the GEMM costs 10-15 % of the GEMM on span
+// masks and 3x on i.i.d. masks, because row tiles that straddle run boundaries need many TMA
+// instructions per k-step.  The copy wins unless the FFN is narrow (h < 2048) and M is large.
+static bool permute_first(int64_t M, int64_t d, int64_t h) {
+  (void)d;
+  static const int forced = [] {
+    const char* e = getenv("FFNK_PERMUTE");
+    return e ? atoi(e) : -1;
+  }();
+  if (forced >= 0) return forced != 0;
+  return M < 2048 || h >= 2048;
+}
+
+struct FfnWorkspace {
+  int64_t perm, counts, scan, xr, inter, total;
+};
+
+static FfnWorkspace ffn_workspace(int64_t M, int64_t d, int64_t h) {
+  FfnWorkspace w{};
+  const int64_t cap = ffnk_route_capacity(M);
+  int64_t off = 0;
+  w.perm = off;
+  off += align256(2 * cap * 4 + 16);
+  w.counts = off;
+  off += 256;
+  w.scan = off;
+  off += align256(ffnk_route_workspace_bytes(M));
+  w.xr = off;
+  if (permute_first(M, d, h)) off += align256((cap + 512) * d * 2);
+  w.inter = off;
+  off += align256((cap + 512) * h * 2);
+  w.total = off;
+  return w;
+}
+
+}  // namespace ffnk
+
+using namespace ffnk;
+
+extern "C" int ffnk_ffn_permute_first(int64_t M, int64_t d, int64_t h) { return permute_first(M, d, h) ? 1 : 0; }
+
+extern "C" int64_t ffnk_ffn_workspace_bytes(int64_t M, int64_t d, int64_t h) {
+  if (M <= 0 || d <= 0 || h <= 0) return 256;
+  return ffn_workspace(M, d, h).total;
+}
+
+extern "C" int ffnk_ffn_forward(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3,
+                                const void* u1, const void* u2, const void* u3, int64_t w13_stride_k,
+                                int64_t w13_stride_n, int64_t w2_stride_k, int64_t w2_stride_n, const void* mask,
+                                void* workspace, int64_t workspace_bytes, void* y, int64_t ldy, int64_t M, int64_t d,
+                                int64_t h, int allow_decode, int32_t* status, void* stream) {
+  if (M == 0) return 0;
+  if (!x || !w1 || !w2 || !w3 || !u1 || !u2 || !u3 || !mask || !workspace || !y || !status) return FFNK_ERR_NULL;
+  if (M < 0 || M >= (1ll << 30) || d < 8 || h < 8 || (d & 7) || (h & 7)) return FFNK_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return FFNK_ERR_ALIGN;
+  const FfnWorkspace w = ffn_workspace(M, d, h);
+  if (workspace_bytes < w.total) return FFNK_ERR_CAPACITY;
+  char* ws = static_cast<char*>(workspace);
+
+  const bool k_major = w13_stride_k == 1 && w2_stride_k == 1;
+  if (allow_decode && M <= ffnk_decode_max_tokens() && k_major)
+    return ffnk_ffn_decode(x, ldx, w1, w2, w3, u1, u2, u3, w13_stride_k, w13_stride_n, w2_stride_k, w2_stride_n, mask,
+                           ws + w.inter, y, ldy, M, d, h, status, stream);
+
+  int32_t* perm = reinterpret_cast<int32_t*>(ws + w.perm);
+  int32_t* counts = reinterpret_cast<int32_t*>(ws + w.counts);
+  int r = ffnk_route(mask, M, perm, counts, ws + w.scan, status, stream);
+  if (r) return r;
+  const void* a = x;
+  int64_t lda = ldx;
+  int routed_in = 0;
+  if (permute_first(M, d, h)) {
+    if ((r = ffnk_permute_rows(x, ldx, perm, counts, ws + w.xr, d, M, d, stream))) return r;
+    a = ws + w.xr;
+    lda = d;
+    routed_in = 1;
+  }
+  if ((r = ffnk_ffn_gateup(a, lda, w1, w3, u1, u3, w13_stride_k, w13_stride_n, perm, counts, ws + w.inter, h,
+                           routed_in, 1, M, d, h, status, stream)))
+    return r;
+  return ffnk_ffn_down(ws + w.inter, h, w2, u2, w2_stride_k, w2_stride_n, perm, counts, y, ldy, M, d, h, status,
+                       stream);
+}

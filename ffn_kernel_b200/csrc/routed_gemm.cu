@@ -144,12 +144,12 @@ __device__ __forceinline__ int text_row_base(int Mv) { return ((Mv + 255) >> 8) 
 // Epilogue of one accumulator row: this thread owns TMEM lane `taddr`'s row, 256 fp32 columns.
 // EPI_STORE : out_row[n_base + c] = bf16(acc[c]),                       256 columns
 // EPI_SWIGLU: out_row[n_base + c] = bf16(silu(acc[c]) * acc[128 + c]),   128 columns
-template <int EPI>
+template <int EPI, int BN_T>
 __device__ __forceinline__ void epilogue_row(uint32_t taddr, __nv_bfloat16* out_row, bool valid, int n_base,
                                              int n_out) {
   if constexpr (EPI == EPI_STORE) {
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = 0; c < BN_T / 32; ++c) {
       uint32_t v[32];
       tmem_ld_32x32(taddr + c * 32, v);
       tmem_ld_wait();
@@ -170,10 +170,10 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, __nv_bfloat16* out_
     }
   } else {
 #pragma unroll 1
-    for (int c = 0; c < BN / 64; ++c) {
+    for (int c = 0; c < BN_T / 64; ++c) {
       uint32_t g[32], u[32];
       tmem_ld_32x32(taddr + c * 32, g);            // gate  (t1)
-      tmem_ld_32x32(taddr + BN / 2 + c * 32, u);   // up    (t3)
+      tmem_ld_32x32(taddr + BN_T / 2 + c * 32, u);   // up    (t3)
       tmem_ld_wait();
       const int n0 = n_base + c * 32;
       if (valid && n0 < n_out) {
@@ -196,16 +196,22 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, __nv_bfloat16* out_
   }
 }
 
-template <int A_MODE, int EPI, int OUT_MODE, bool B_MN>
+// BN_T = 256 is the throughput tile; BN_T = 64 (K-major weights only) spreads a problem with few row
+// tiles over more SMs: 8 stages of 24 KiB, four times as many column tiles.
+template <int A_MODE, int EPI, int OUT_MODE, bool B_MN, int BN_T>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUtensorMap tmBv0,
                    const __grid_constant__ CUtensorMap tmBv1, const __grid_constant__ CUtensorMap tmBt0,
                    const __grid_constant__ CUtensorMap tmBt1, const GemmParams p) {
+  static_assert(BN_T == 256 || (BN_T == 64 && !B_MN), "64-column tiles exist for K-major weights only");
+  constexpr int TB_BYTES = BN_T * BK * 2;
+  constexpr int TSTAGE_BYTES = A_BYTES + TB_BYTES;
+  constexpr int TSTAGES = (BN_T == 256) ? STAGES : 8;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-  uint64_t* empty = full + STAGES;
-  uint64_t* tfull = empty + STAGES;   // accumulator ready for the epilogue   [2]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + TSTAGES * TSTAGE_BYTES);
+  uint64_t* empty = full + TSTAGES;
+  uint64_t* tfull = empty + TSTAGES;   // accumulator ready for the epilogue   [2]
   uint64_t* tempty = tfull + 2;       // accumulator drained by the epilogue  [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -214,7 +220,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < TSTAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -242,7 +248,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
   const int Mv = p.counts[0], Mt = p.counts[1], cap = p.counts[2];
   const int tiles_v = (Mv + BM - 1) / BM;
   const int m_tiles = tiles_v + (Mt + BM - 1) / BM;
-  constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN_T / 2 : BN_T;
   const int n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
   const int total_tiles = m_tiles * n_tiles;
   const int k_steps = (p.k_len + BK - 1) / BK;
@@ -284,9 +290,9 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
           ok = false;
           break;
         }
-        uint8_t* sa = smem + stage * STAGE_BYTES;
+        uint8_t* sa = smem + stage * TSTAGE_BYTES;
         uint8_t* sb = sa + A_BYTES;
-        if (lane == 0) mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+        if (lane == 0) mbar_arrive_expect_tx(&full[stage], TSTAGE_BYTES);
         __syncwarp();
         const int kx = ks * BK;
         if constexpr (A_MODE == A_GATHER) {
@@ -299,31 +305,31 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
         if (lane == 0) {
           if constexpr (!B_MN) {
             // K-major weights: two boxes of 128 weight rows x 64 k
-            const int n0 = (EPI == EPI_SWIGLU) ? tc.nt * (BN / 2) : tc.nt * BN;
-            const int n1 = (EPI == EPI_SWIGLU) ? n0 : n0 + BN / 2;
+            const int n0 = (EPI == EPI_SWIGLU) ? tc.nt * (BN_T / 2) : tc.nt * BN_T;
+            const int n1 = (EPI == EPI_SWIGLU) ? n0 : n0 + BN_T / 2;
             tma_load_2d(sb, mB0, &full[stage], kx, n0);
-            tma_load_2d(sb + B_BYTES / 2, mB1, &full[stage], kx, n1);
+            tma_load_2d(sb + TB_BYTES / 2, mB1, &full[stage], kx, n1);
           } else {
             // MN-major weights: four boxes of 64 k rows x 64 output columns
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const CUtensorMap* m = (EPI == EPI_SWIGLU && j >= 2) ? mB1 : mB0;
-              const int n = (EPI == EPI_SWIGLU) ? tc.nt * (BN / 2) + (j & 1) * 64 : tc.nt * BN + j * 64;
-              tma_load_2d(sb + j * (B_BYTES / 4), m, &full[stage], n, kx);
+              const int n = (EPI == EPI_SWIGLU) ? tc.nt * (BN_T / 2) + (j & 1) * 64 : tc.nt * BN_T + j * 64;
+              tma_load_2d(sb + j * (TB_BYTES / 4), m, &full[stage], n, kx);
             }
           }
         }
         ++issued;
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == TSTAGES) { stage = 0; phase ^= 1; }
       }
     }
     if (*abort_flag && lane == 0) {
       // let the copies already issued land before the CTA gives its shared memory back
       int s = stage;
       uint32_t ph = phase;
-      const int n = issued < STAGES ? issued : STAGES;
+      const int n = issued < TSTAGES ? issued : TSTAGES;
       for (int i = 0; i < n; ++i) {
-        if (--s < 0) { s = STAGES - 1; ph ^= 1; }
+        if (--s < 0) { s = TSTAGES - 1; ph ^= 1; }
         int dummy = 0;
         mbar_wait(&full[s], ph, &dummy, 1000000ull);
       }
@@ -331,7 +337,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, false, B_MN);
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN_T, false, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -344,7 +350,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
+        const uint32_t tmem_d = tmem_base + acc * BN_T;
         for (int ks = 0; ks < k_steps; ++ks) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             report(p.status, ST_TIMEOUT_MMA_FULL);
@@ -352,17 +358,17 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t a_addr = smem_u32(smem + stage * TSTAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t da = umma_smem_desc(a_addr + kk * (UMMA_K * 2), 16, 1024);
-            const uint64_t db = B_MN ? umma_smem_desc(b_addr + kk * (UMMA_K * 128), B_BYTES / 4, 1024)
+            const uint64_t db = B_MN ? umma_smem_desc(b_addr + kk * (UMMA_K * 128), TB_BYTES / 4, 1024)
                                      : umma_smem_desc(b_addr + kk * (UMMA_K * 2), 16, 1024);
             umma_bf16<1>(tmem_d, da, db, idesc, (ks | kk) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == TSTAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tfull[acc]);
       }
@@ -391,9 +397,9 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN_T;
       __nv_bfloat16* out_row = p.out + dst_row * p.ldo;
-      epilogue_row<EPI>(taddr, out_row, valid, tc.nt * (EPI == EPI_SWIGLU ? BN / 2 : BN), p.n_out);
+      epilogue_row<EPI, BN_T>(taddr, out_row, valid, tc.nt * (EPI == EPI_SWIGLU ? BN_T / 2 : BN_T), p.n_out);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -655,7 +661,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_row<EPI>(taddr, p.out + dst_row * p.ldo, valid, tc.nt * N_PER_TILE, p.n_out);
+      epilogue_row<EPI, BN>(taddr, p.out + dst_row * p.ldo, valid, tc.nt * N_PER_TILE, p.n_out);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
@@ -954,10 +960,10 @@ struct WeightView {
 };
 
 // Tensor map over one weight for the B operand.  K-major: storage rows are output columns.
-static int weight_map(CUtensorMap* m, const WeightView& w, bool* mn_major) {
+static int weight_map(CUtensorMap* m, const WeightView& w, bool* mn_major, int box_rows = BN / 2) {
   if (w.stride_k == 1 && (w.stride_n >= w.K || w.N == 1)) {
     *mn_major = false;
-    return make_tensor_map_2d(m, w.base, w.K, w.N, w.stride_n, BK, BN / 2);
+    return make_tensor_map_2d(m, w.base, w.K, w.N, w.stride_n, BK, box_rows);
   }
   if (w.stride_n == 1 && (w.stride_k >= w.N || w.K == 1)) {
     *mn_major = true;
@@ -1006,25 +1012,50 @@ static int pick_group_m(int64_t k_len) {
 // Tile table (replaces the reference's JSON lookup, ffn_kernel/utils.py:3-5): CTA pairs with
 // 256-row tiles once there are enough rows to fill them, single CTAs with 128-row tiles below.
 // FFNK_PAIR=0/1 overrides the choice for experiments.
-static bool use_pair_tiles(int64_t M, int a_mode, int epi) {
-  static const int forced = [] {
-    const char* e = getenv("FFNK_PAIR");
-    return e ? atoi(e) : -1;
-  }();
-  if (forced >= 0) return forced != 0;
-  // measured at d=4096/h=11008, M=16384: pairs gain ~4% when A arrives as one box per tile and the
-  // epilogue is a plain store (down projection), and lose ~3% under the two-weight SwiGLU tile
-  return M >= 4096 && a_mode == A_ROUTED && epi == EPI_STORE;
+// Tile table (replaces the reference's JSON lookup, ffn_kernel/utils.py:3-5).
+//   pair   : CTA pairs, 256-row tiles.  Measured at d=4096/h=11008, M=16384: +4 % when A arrives as one
+//            box per tile and the epilogue is a plain store (down projection), -3 % under the
+//            two-weight SwiGLU tile, so it is used for the former only, from M = 4096.
+//   narrow : single CTAs with 64 accumulator columns, for problems with so few row tiles that 256-wide
+//            tiles would leave most SMs idle (small M: the weights then stream through 4x as many CTAs).
+//   else   : single CTAs, 128 x 256 tiles.
+// FFNK_PAIR=0/1 and FFNK_NARROW=0/1 override the choice for experiments.
+struct TileChoice {
+  bool pair;
+  int bn;   // accumulator columns per tile
+};
+
+static int env_flag(const char* name) {
+  const char* e = getenv(name);
+  return e ? atoi(e) : -1;
 }
+
+static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool k_major_weights) {
+  static const int force_pair = env_flag("FFNK_PAIR");
+  static const int force_narrow = env_flag("FFNK_NARROW");
+  TileChoice t{false, BN};
+  const bool pair = force_pair >= 0 ? force_pair != 0 : (M >= 4096 && a_mode == A_ROUTED && epi == EPI_STORE);
+  if (pair) {
+    t.pair = true;
+    return t;
+  }
+  const int64_t n_per_tile = (epi == EPI_SWIGLU) ? BN / 2 : BN;
+  const int64_t wide_tiles = ((M + BM - 1) / BM + 1) * ((n_out + n_per_tile - 1) / n_per_tile);
+  const bool narrow = force_narrow >= 0 ? force_narrow != 0 : wide_tiles < device_info().sm_count;
+  if (narrow && k_major_weights) t.bn = 64;
+  return t;
+}
+
+static bool weights_k_major(int64_t stride_k, int64_t stride_n, int64_t K) { return stride_k == 1 && stride_n >= K; }
 
 template <int A_MODE, int EPI, int OUT_MODE>
 static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn, const GemmParams& p,
-                       int64_t M, cudaStream_t stream) {
+                       int64_t M, TileChoice tile, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
-  constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
-  const int64_t n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
-  if (use_pair_tiles(M, A_MODE, EPI)) {
+  const int n_per_tile = (EPI == EPI_SWIGLU) ? tile.bn / 2 : tile.bn;
+  const int64_t n_tiles = (p.n_out + n_per_tile - 1) / n_per_tile;
+  if (tile.pair) {
     int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
     if (pairs > usable_sms(dev) / 2) pairs = usable_sms(dev) / 2;
     if (pairs < 1) pairs = 1;
@@ -1057,8 +1088,9 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
     kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
     return cuda_status(cudaGetLastError());
   };
-  return b_mn ? go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, true>)
-              : go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false>);
+  if (tile.bn == 64) return go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false, 64>);
+  return b_mn ? go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, true, BN>)
+              : go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false, BN>);
 }
 
 static bool bad_dim(int64_t v) { return v < 8 || (v & 7) || v >= (1ll << 30); }
@@ -1079,13 +1111,14 @@ extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const
   int r = gather_maps(tmA, a, K, M, lda);
   if (r) return r;
   bool mn1 = false, mn2 = false;
-  if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_k, b_stride_n, K, N}, &mn1))) return r;
-  if ((r = weight_map(&tmB[2], WeightView{b2, b_stride_k, b_stride_n, K, N}, &mn2))) return r;
+  const TileChoice tile = pick_tile(M, N, A_GATHER, EPI_STORE, weights_k_major(b_stride_k, b_stride_n, K));
+  if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_k, b_stride_n, K, N}, &mn1, tile.bn / 2))) return r;
+  if ((r = weight_map(&tmB[2], WeightView{b2, b_stride_k, b_stride_n, K, N}, &mn2, tile.bn / 2))) return r;
   tmB[1] = tmB[0];
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(c), ldc, static_cast<int>(N), static_cast<int>(K),
                static_cast<int>(M), pick_group_m(K), max_run_rows(), status, g_prof_buffer};
-  return launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, static_cast<cudaStream_t>(stream));
+  return launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1,
@@ -1109,18 +1142,20 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
   if (r) return r;
   bool mn = false, mn_i = false;
   const void* ws[4] = {w1, w3, u1, u3};
+  const TileChoice tile = pick_tile(M, h, routed_in ? A_ROUTED : A_GATHER, EPI_SWIGLU,
+                                    weights_k_major(w_stride_k, w_stride_n, d));
   for (int i = 0; i < 4; ++i) {
-    if ((r = weight_map(&tmB[i], WeightView{ws[i], w_stride_k, w_stride_n, d, h}, &mn_i))) return r;
+    if ((r = weight_map(&tmB[i], WeightView{ws[i], w_stride_k, w_stride_n, d, h}, &mn_i, tile.bn / 2))) return r;
     mn = mn_i;
   }
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(out), ldo, static_cast<int>(h), static_cast<int>(d),
                static_cast<int>(M), pick_group_m(d), max_run_rows(), status, g_prof_buffer};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (routed_in)
-    return routed_out ? launch_gemm<A_ROUTED, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, M, s)
-                      : launch_gemm<A_ROUTED, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, M, s);
-  return routed_out ? launch_gemm<A_GATHER, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, M, s)
-                    : launch_gemm<A_GATHER, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, M, s);
+    return routed_out ? launch_gemm<A_ROUTED, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, M, tile, s)
+                      : launch_gemm<A_ROUTED, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, M, tile, s);
+  return routed_out ? launch_gemm<A_GATHER, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, M, tile, s)
+                    : launch_gemm<A_GATHER, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, M, tile, s);
 }
 
 extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
@@ -1137,13 +1172,14 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   if (r) return r;
   for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
   bool mn1 = false, mn2 = false;
-  if ((r = weight_map(&tmB[0], WeightView{w2, w_stride_k, w_stride_n, h, d}, &mn1))) return r;
-  if ((r = weight_map(&tmB[2], WeightView{u2, w_stride_k, w_stride_n, h, d}, &mn2))) return r;
+  const TileChoice tile = pick_tile(M, d, A_ROUTED, EPI_STORE, weights_k_major(w_stride_k, w_stride_n, h));
+  if ((r = weight_map(&tmB[0], WeightView{w2, w_stride_k, w_stride_n, h, d}, &mn1, tile.bn / 2))) return r;
+  if ((r = weight_map(&tmB[2], WeightView{u2, w_stride_k, w_stride_n, h, d}, &mn2, tile.bn / 2))) return r;
   tmB[1] = tmB[0];
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(y), ldy, static_cast<int>(d), static_cast<int>(h),
                static_cast<int>(M), pick_group_m(h), max_run_rows(), status, g_prof_buffer};
-  return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, static_cast<cudaStream_t>(stream));
+  return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
@@ -1178,13 +1214,14 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     int r = gather_maps(tmA, g, N, M, ldg);
     if (r) return r;
     bool mn1 = false, mn2 = false;
-    if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_n, b_stride_k, N, K}, &mn1))) return r;
-    if ((r = weight_map(&tmB[2], WeightView{b2, b_stride_n, b_stride_k, N, K}, &mn2))) return r;
+    const TileChoice tile = pick_tile(M, K, A_GATHER, EPI_STORE, weights_k_major(b_stride_n, b_stride_k, N));
+    if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_n, b_stride_k, N, K}, &mn1, tile.bn / 2))) return r;
+    if ((r = weight_map(&tmB[2], WeightView{b2, b_stride_n, b_stride_k, N, K}, &mn2, tile.bn / 2))) return r;
     tmB[1] = tmB[0];
     tmB[3] = tmB[2];
     GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(da), ldda, static_cast<int>(K), static_cast<int>(N),
                  static_cast<int>(M), pick_group_m(N), max_run_rows(), status, g_prof_buffer};
-    r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, s);
+    r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, s);
     if (r) return r;
   }
   // dW: output in the weight's storage order; P supplies the storage rows, Q the storage columns

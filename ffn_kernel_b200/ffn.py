@@ -51,16 +51,9 @@ def _phase(name: str) -> None:
 
 
 def permute_rows_first(M: int, d: int, h: int) -> bool:
-    """Tile-table entry for the FFN forward: copy x into routed order before the gate/up GEMM?
-
-    The copy moves 4*M*d bytes through HBM; the gate/up GEMM does 4*M*d*h FLOP.  With the GEMM
-    near 1.3 PFLOP/s and the copy near 5 TB/s the copy costs about 260/h of the GEMM time, while
-    gathering inside the GEMM costs 10-15 % on span masks and 3x on i.i.d. masks (row tiles that
-    straddle run boundaries need many TMA instructions per k-step).  FFNK_PERMUTE=0/1 overrides."""
-    forced = os.environ.get("FFNK_PERMUTE")
-    if forced is not None:
-        return forced != "0"
-    return M >= 2048 and h >= 2048
+    """Tile-table entry of the library for the FFN forward: is x copied into routed order before
+    the gate/up GEMM for this shape?  (FFNK_PERMUTE=0/1 overrides, read once per process.)"""
+    return bool(lib().ffnk_ffn_permute_first(M, d, h))
 
 
 def decode_max_tokens() -> int:
@@ -86,7 +79,26 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
         if M == 0:
             return y
         st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
-        if allow_decode and rt is None and M <= decode_max_tokens():
+        if rt is None and PHASE_HOOK is None:
+            # the normal path: one call into the library does routing, permutation and both GEMMs
+            # (or the decode kernels) out of one workspace allocation
+            if mask.dim() != 1 or mask.shape[0] != M or mask.device != dev:
+                raise RuntimeError(f"mask must have shape [{M}] on {dev}")
+            if mask.dtype not in (torch.bool, torch.uint8):
+                raise RuntimeError(f"mask must be torch.bool (or uint8), got {mask.dtype}")
+            m8 = mask.contiguous()
+            nbytes = int(L.ffnk_ffn_workspace_bytes(M, d, h))
+            ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+            check("ffnk_ffn_forward", L.ffnk_ffn_forward(
+                x.data_ptr(), x.stride(0), w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), u1.data_ptr(),
+                u2.data_ptr(), u3.data_ptr(), w1.stride(0), w1.stride(1), w2.stride(0), w2.stride(1),
+                m8.data_ptr(), ws.data_ptr(), nbytes, y.data_ptr(), y.stride(0), M, d, h,
+                1 if allow_decode else 0, st, sp))
+            maybe_check(dev)
+            return y
+        # step by step (an observer wants the phase boundaries, or the caller brings routing lists)
+        if (allow_decode and rt is None and M <= decode_max_tokens() and w1.stride(0) == 1
+                and w2.stride(0) == 1):
             if mask.dim() != 1 or mask.shape[0] != M or mask.device != dev:
                 raise RuntimeError(f"mask must have shape [{M}] on {dev}")
             m8 = mask.contiguous()

@@ -142,8 +142,14 @@ def main():
         t = timeit(down, a.iters, a.warmup)
         emit(kernel="ffn_down", M=M, d=d, h=h, mask=a.mask, ms=t, tflops=2 * M * d * h / t / 1e9)
         t = timeit(lambda: _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False), a.iters, a.warmup)
-        emit(kernel="ffn_forward(route+gateup+down)", M=M, d=d, h=h, mask=a.mask, ms=t,
-             tflops=6 * M * d * h / t / 1e9)
+        emit(kernel="ffn_forward(Python API, one library call)", M=M, d=d, h=h, mask=a.mask, ms=t,
+             tflops=6 * M * d * h / t / 1e9, weight_gbs=6 * d * h * 2 / t / 1e6)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)
+        t = timeit(g.replay, a.iters, a.warmup)
+        emit(kernel="ffn_forward(CUDA graph replay)", M=M, d=d, h=h, mask=a.mask, ms=t,
+             tflops=6 * M * d * h / t / 1e9, weight_gbs=6 * d * h * 2 / t / 1e6)
     elif a.what == "linear":
         M, K, N = a.M, a.K, a.N
         c = linear_case(M, K, N, seed=0, mask=edge_mask(M, a.mask, 0), with_grad=True).to(dev)

@@ -153,6 +153,22 @@ int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, 
                     int64_t w2_stride_n, const void* mask, void* inter, void* y, int64_t ldy, int64_t M, int64_t d,
                     int64_t h, int32_t* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * The whole MaskedFFN forward in one call (MaskedFFN.forward, ffn_kernel/ops.py:28-32):
+ * routing, optional row permutation, gate/up, down -- or the decode kernels when
+ * allow_decode != 0, M <= ffnk_decode_max_tokens() and the weights are K-major.
+ * workspace: ffnk_ffn_workspace_bytes(M, d, h) bytes of device memory, 256-byte aligned, owned by
+ * the caller and reusable as soon as the stream has passed this call; too small a workspace
+ * returns FFNK_ERR_CAPACITY.  ffnk_ffn_permute_first() tells whether the tile table copies x
+ * into routed order first for this shape.
+ * ------------------------------------------------------------------------------------- */
+int64_t ffnk_ffn_workspace_bytes(int64_t M, int64_t d, int64_t h);
+int ffnk_ffn_permute_first(int64_t M, int64_t d, int64_t h);
+int ffnk_ffn_forward(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
+                     const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n, int64_t w2_stride_k,
+                     int64_t w2_stride_n, const void* mask, void* workspace, int64_t workspace_bytes, void* y,
+                     int64_t ldy, int64_t M, int64_t d, int64_t h, int allow_decode, int32_t* status, void* stream);
+
 /* Synchronises `stream`, copies the status word to the host and returns it (0 = ok, >0 one of
  * the device status codes, <0 an error as above).  If `clear` is non-zero the word is reset to 0. */
 int ffnk_read_status(int32_t* status, int clear, void* stream);

@@ -129,3 +129,40 @@ def test_full_size_rows_sampled(dev):
     assert bool(torch.isfinite(y.float()).all())
     sub = MaskedFFN.apply(g.x[rows.to(dev)], *g.apply_args()[1:7], g.mask[rows.to(dev)])
     assert O.max_rel_err(sub, y[rows.to(dev)].float()) < 1e-2
+
+
+@pytest.mark.parametrize("M", [5, 300, 4099])
+def test_single_call_and_step_by_step_paths_agree(dev, M):
+    from ffn_kernel_b200 import route
+    c = ffn_case(M, 256, 520, seed=M, mask=edge_mask(M, "bernoulli", 4)).to(dev)
+    y_one = _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)
+    y_steps = _bf16_ffn_fused_forward(*c.apply_args(), rt=route(c.mask), allow_decode=False)
+    check_status()
+    assert torch.equal(y_one, y_steps)
+
+
+@pytest.mark.parametrize("M", [1, 8])
+def test_small_token_counts_with_contiguous_weights(dev, M):
+    # the decode kernels stream K-major rows only; other layouts take the GEMM path
+    c = ffn_case(M, 256, 520, seed=M, mask=edge_mask(M, "alternating"))
+    ref = O.masked_ffn(*c.apply_args())
+    g = c.to(dev)
+    args = [g.x] + [w.T.contiguous() for w in (g.w1, g.w2, g.w3, g.u1, g.u2, g.u3)] + [g.mask]
+    y = MaskedFFN.apply(*args)
+    check_status()
+    assert O.max_rel_err(y, ref) < TOL
+
+
+def test_single_call_rejects_a_short_workspace(dev):
+    from ffn_kernel_b200._lib import lib
+    from ffn_kernel_b200.route import status_word, stream_ptr
+    L = lib()
+    M, d, h = 300, 256, 520
+    c = ffn_case(M, d, h, seed=1).to(dev)
+    need = int(L.ffnk_ffn_workspace_bytes(M, d, h))
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    y = torch.empty(M, d, dtype=torch.bfloat16, device=dev)
+    rc = L.ffnk_ffn_forward(c.x.data_ptr(), d, c.w1.data_ptr(), c.w2.data_ptr(), c.w3.data_ptr(), c.u1.data_ptr(),
+                            c.u2.data_ptr(), c.u3.data_ptr(), 1, d, 1, h, c.mask.data_ptr(), ws.data_ptr(), need - 256,
+                            y.data_ptr(), d, M, d, h, 1, status_word(dev).data_ptr(), stream_ptr(dev))
+    assert rc == -8
