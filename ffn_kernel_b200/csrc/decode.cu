@@ -1,12 +1,12 @@
-// Small-M (decode) MaskedFFN forward: a weight-streaming kernel pair for M <= 8 tokens.
+// Small-M (decode) MaskedFFN forward: a weight-streaming kernel pair for M <= 32 tokens.
 //
 // With a handful of tokens the FFN is a matrix-vector product: every weight of each modality
 // that is present is read exactly once (3*d*h bf16 per modality) and the arithmetic is tiny,
 // so the kernels are built around the HBM stream, not around a 128-row tensor tile:
 //   * every lane fetches weights with 128-bit loads straight from the weight's own storage
 //     (K-major, the nn.Linear.weight.T view); nothing is staged through shared memory;
-//   * the tokens of the modality form the N = 8 side of mma.sync.m16n8k16 (bf16 in, fp32
-//     accumulate).  The k-slots of the instruction are assigned so that one 16-byte chunk of a
+//   * the tokens of the modality, in groups of eight, form the N = 8 side of mma.sync.m16n8k16
+//     (bf16 in, fp32 accumulate; up to 4 groups per CTA, each weight fragment reused by all).  The k-slots of the instruction are assigned so that one 16-byte chunk of a
 //     weight row and the same 16-byte chunk of a token row feed two MMAs directly from
 //     registers, with no shuffles: lane (g, t) of the warp holds chunk t of rows g and g+8;
 //   * the contraction is split over the warps of a CTA (8 for gate/up, 16 for down) and summed
@@ -26,7 +26,9 @@
 
 namespace ffnk {
 
-constexpr int kDecodeMaxTokens = 8;
+// Beyond ~32 tokens the token rows (re-read by every CTA) outweigh the weight stream and the
+// tcgen05 GEMM path is faster (measured at d=1024/h=2816: 16 tokens 17 us, 64 tokens 45 us against 39 us).
+constexpr int kDecodeMaxTokens = 32;
 constexpr int kDecodeRows = 16;   // weight rows per CTA (the M side of m16n8k16)
 
 __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
@@ -63,10 +65,13 @@ struct DecodeParams {
 
 // GATEUP: out[tok, r] = silu(x[tok] . wa[r]) * (x[tok] . wb[r]);  otherwise out[tok, r] = x[tok] . wa[r]
 // WAIT_PRIMARY: this launch depends on the previous kernel in the stream for `x`.
-template <bool GATEUP, bool WAIT_PRIMARY, int WARPS, int UNROLL>
+// G: token groups of eight (the N side of the MMA) a CTA can hold; the modality's tokens fill
+//    them in order and empty groups are skipped.
+template <bool GATEUP, bool WAIT_PRIMARY, int WARPS, int UNROLL, int G>
 __global__ void __launch_bounds__(WARPS * 32) decode_phase_kernel(const DecodeParams p) {
-  __shared__ float red[WARPS][32][GATEUP ? 8 : 4];
-  __shared__ int s_tok[kDecodeMaxTokens];
+  constexpr int ACC = GATEUP ? 8 : 4;
+  __shared__ float red[G][32][ACC];
+  __shared__ int s_tok[G * 8];
   __shared__ int s_ntok;
 
   const int modality = blockIdx.y;          // 0: mask != 0 (first weight set), 1: mask == 0
@@ -74,16 +79,24 @@ __global__ void __launch_bounds__(WARPS * 32) decode_phase_kernel(const DecodePa
   const int g = lane >> 2, t = lane & 3;
   if constexpr (!WAIT_PRIMARY) pdl_launch_dependents();
 
+  for (int i = threadIdx.x; i < G * 32 * ACC; i += WARPS * 32) (&red[0][0][0])[i] = 0.f;
   if (warp == 0) {
-    // one mask byte per lane, all loads in flight together; the modality's tokens keep their order
-    const bool mine = lane < p.M && ((p.mask[lane] != 0) == (modality == 0));
-    const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, mine);
-    if (mine) s_tok[__popc(ballot & ((1u << lane) - 1u))] = lane;
-    if (lane == 0) s_ntok = __popc(ballot);
+    // 32 mask bytes per round, all loads of a round in flight together; token order is kept
+    int base = 0;
+#pragma unroll
+    for (int r = 0; r < (G * 8 + 31) / 32; ++r) {
+      const int idx = r * 32 + lane;
+      const bool mine = idx < p.M && ((p.mask[idx] != 0) == (modality == 0));
+      const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, mine);
+      if (mine) s_tok[base + __popc(ballot & ((1u << lane) - 1u))] = idx;
+      base += __popc(ballot);
+    }
+    if (lane == 0) s_ntok = base;
   }
   __syncthreads();
   const int ntok = s_ntok;
   if (ntok == 0) return;
+  const int ngroups = (ntok + 7) >> 3;
 
   const int r0 = blockIdx.x * kDecodeRows;
   const int row_lo = r0 + g, row_hi = r0 + g + 8;
@@ -92,17 +105,28 @@ __global__ void __launch_bounds__(WARPS * 32) decode_phase_kernel(const DecodePa
   const __nv_bfloat16* wa_hi = p.wa[modality] + static_cast<int64_t>(hi_ok ? row_hi : 0) * p.ldw;
   const __nv_bfloat16* wb_lo = GATEUP ? p.wb[modality] + static_cast<int64_t>(lo_ok ? row_lo : 0) * p.ldw : nullptr;
   const __nv_bfloat16* wb_hi = GATEUP ? p.wb[modality] + static_cast<int64_t>(hi_ok ? row_hi : 0) * p.ldw : nullptr;
-  const bool tok_ok = g < ntok;
-  const __nv_bfloat16* xrow = p.x + static_cast<int64_t>(tok_ok ? s_tok[g] : 0) * p.ldx;
+  // this lane supplies token slot g of every group
+  const __nv_bfloat16* xrow[G];
+#pragma unroll
+  for (int gi = 0; gi < G; ++gi) {
+    const int slot = gi * 8 + g;
+    xrow[gi] = slot < ntok ? p.x + static_cast<int64_t>(s_tok[slot]) * p.ldx : nullptr;
+  }
 
-  float acc_a[4] = {0.f, 0.f, 0.f, 0.f};
-  float acc_b[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc_a[G][4], acc_b[GATEUP ? G : 1][4];
+#pragma unroll
+  for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc_a[gi][i] = 0.f;
+      if (GATEUP) acc_b[gi][i] = 0.f;
+    }
   const uint4 zero = make_uint4(0, 0, 0, 0);
   const int kblocks = (p.K + 31) / 32;      // 32 contraction elements per step: 4 lanes x 16 bytes per row
 
   bool waited = !WAIT_PRIMARY;
   for (int kb0 = warp; kb0 < kblocks; kb0 += WARPS * UNROLL) {
-    uint4 a_lo[UNROLL], a_hi[UNROLL], b_lo[UNROLL], b_hi[UNROLL], xv[UNROLL];
+    uint4 a_lo[UNROLL], a_hi[UNROLL], b_lo[GATEUP ? UNROLL : 1], b_hi[GATEUP ? UNROLL : 1];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (kb0 + u * WARPS) * 32 + t * 8;
@@ -119,48 +143,50 @@ __global__ void __launch_bounds__(WARPS * 32) decode_phase_kernel(const DecodePa
       waited = true;
     }
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int k = (kb0 + u * WARPS) * 32 + t * 8;
-      const bool k_ok = (kb0 + u * WARPS) < kblocks && k < p.K;
-      xv[u] = (k_ok && tok_ok) ? *reinterpret_cast<const uint4*>(xrow + k) : zero;
-    }
+    for (int gi = 0; gi < G; ++gi) {
+      if (gi < ngroups) {
+        uint4 xv[UNROLL];
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      mma_bf16_16x8x16(acc_a, a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, xv[u].x, xv[u].y);
-      mma_bf16_16x8x16(acc_a, a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, xv[u].z, xv[u].w);
-      if constexpr (GATEUP) {
-        mma_bf16_16x8x16(acc_b, b_lo[u].x, b_hi[u].x, b_lo[u].y, b_hi[u].y, xv[u].x, xv[u].y);
-        mma_bf16_16x8x16(acc_b, b_lo[u].z, b_hi[u].z, b_lo[u].w, b_hi[u].w, xv[u].z, xv[u].w);
+        for (int u = 0; u < UNROLL; ++u) {
+          const int k = (kb0 + u * WARPS) * 32 + t * 8;
+          const bool k_ok = (kb0 + u * WARPS) < kblocks && k < p.K;
+          xv[u] = (k_ok && xrow[gi] != nullptr) ? *reinterpret_cast<const uint4*>(xrow[gi] + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          mma_bf16_16x8x16(acc_a[gi], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, xv[u].x, xv[u].y);
+          mma_bf16_16x8x16(acc_a[gi], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, xv[u].z, xv[u].w);
+          if constexpr (GATEUP) {
+            mma_bf16_16x8x16(acc_b[gi], b_lo[u].x, b_hi[u].x, b_lo[u].y, b_hi[u].y, xv[u].x, xv[u].y);
+            mma_bf16_16x8x16(acc_b[gi], b_lo[u].z, b_hi[u].z, b_lo[u].w, b_hi[u].w, xv[u].z, xv[u].w);
+          }
+        }
       }
     }
   }
   if (!waited) pdl_wait_primary();
 
-  // sum the partial products of the warps
+  // sum the partial products of the warps in shared memory
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    red[warp][lane][i] = acc_a[i];
-    if constexpr (GATEUP) red[warp][lane][4 + i] = acc_b[i];
-  }
-  __syncthreads();
-  if (warp == 0) {
-    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
+  for (int gi = 0; gi < G; ++gi) {
+    if (gi < ngroups) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        sa[i] += red[w][lane][i];
-        if constexpr (GATEUP) sb[i] += red[w][lane][4 + i];
+        atomicAdd(&red[gi][lane][i], acc_a[gi][i]);
+        if constexpr (GATEUP) atomicAdd(&red[gi][lane][4 + i], acc_b[gi][i]);
       }
     }
-    // accumulator element i: row (g + 8 * (i >> 1)), token slot (2 t + (i & 1))
+  }
+  __syncthreads();
+  for (int gi = warp; gi < ngroups; gi += WARPS) {
+    // accumulator element i: row (g + 8 * (i >> 1)), token slot (2 t + (i & 1)) of the group
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = r0 + g + 8 * (i >> 1);
-      const int slot = 2 * t + (i & 1);
+      const int slot = gi * 8 + 2 * t + (i & 1);
       if (row < p.rows && slot < ntok) {
-        float v = sa[i];
-        if constexpr (GATEUP) v = v * __frcp_rn(1.0f + __expf(-v)) * sb[i];
+        float v = red[gi][lane][i];
+        if constexpr (GATEUP) v = v * __frcp_rn(1.0f + __expf(-v)) * red[gi][lane][4 + i];
         p.out[static_cast<int64_t>(s_tok[slot]) * p.ldo + row] = __float2bfloat16_rn(v);
       }
     }
@@ -223,9 +249,12 @@ extern "C" int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const
   p1.M = static_cast<int>(M);
   p1.K = static_cast<int>(d);
   p1.rows = static_cast<int>(h);
-  cudaError_t e = launch_phase(decode_phase_kernel<true, false, 8, 4>,
-                               dim3(static_cast<unsigned>((h + kDecodeRows - 1) / kDecodeRows), 2), 8 * 32, false,
-                               stream, p1);
+  const dim3 grid1(static_cast<unsigned>((h + kDecodeRows - 1) / kDecodeRows), 2);
+  const int groups = static_cast<int>((M + 7) / 8);   // upper bound: every token in one modality
+  cudaError_t e;
+  if (groups <= 1) e = launch_phase(decode_phase_kernel<true, false, 8, 4, 1>, grid1, 8 * 32, false, stream, p1);
+  else if (groups <= 2) e = launch_phase(decode_phase_kernel<true, false, 8, 4, 2>, grid1, 8 * 32, false, stream, p1);
+  else e = launch_phase(decode_phase_kernel<true, false, 8, 4, 4>, grid1, 8 * 32, false, stream, p1);
   if (e != cudaSuccess) return cuda_status(e);
 
   DecodeParams p2{};
@@ -241,7 +270,9 @@ extern "C" int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const
   p2.M = static_cast<int>(M);
   p2.K = static_cast<int>(h);
   p2.rows = static_cast<int>(d);
-  e = launch_phase(decode_phase_kernel<false, true, 16, 6>,
-                   dim3(static_cast<unsigned>((d + kDecodeRows - 1) / kDecodeRows), 2), 16 * 32, true, stream, p2);
+  const dim3 grid2(static_cast<unsigned>((d + kDecodeRows - 1) / kDecodeRows), 2);
+  if (groups <= 1) e = launch_phase(decode_phase_kernel<false, true, 16, 6, 1>, grid2, 16 * 32, true, stream, p2);
+  else if (groups <= 2) e = launch_phase(decode_phase_kernel<false, true, 16, 6, 2>, grid2, 16 * 32, true, stream, p2);
+  else e = launch_phase(decode_phase_kernel<false, true, 16, 4, 4>, grid2, 16 * 32, true, stream, p2);
   return cuda_status(e);
 }

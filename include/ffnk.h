@@ -145,7 +145,7 @@ int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2
 /* ---------------------------------------------------------------------------------------
  * Small-M (decode) MaskedFFN forward: streams each present modality's weights once with
  * 128-bit loads; same contract as MaskedFFN.forward (ffn_kernel/ops.py:28-32).
- * inter: scratch fp32 [M, h].  Supported for M <= ffnk_decode_max_tokens().
+ * inter: scratch bf16 [M, h].  Supported for M <= ffnk_decode_max_tokens() (32) and K-major weights.
  * ------------------------------------------------------------------------------------- */
 int ffnk_decode_max_tokens(void);
 int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,

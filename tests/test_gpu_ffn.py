@@ -47,7 +47,19 @@ def test_edge_and_decode_sweep(dev, M, kind):
     assert O.max_rel_err(y, ref) < TOL
 
 
-@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("M", [9, 16, 17, 24, 25, 32])
+@pytest.mark.parametrize("kind", ["all_visual", "all_text", "alternating", "bernoulli"])
+def test_decode_kernels_token_groups(dev, M, kind):
+    # more than eight tokens: several groups of eight per modality, partly filled last group
+    assert M <= decode_max_tokens()
+    c = ffn_case(M, 264, 520, seed=M, mask=edge_mask(M, kind, seed=2))
+    ref = O.masked_ffn(*c.apply_args())
+    y = _bf16_ffn_fused_forward(*c.to(dev).apply_args())
+    check_status()
+    assert O.max_rel_err(y, ref) < TOL
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 20, 32])
 def test_decode_and_gemm_paths_agree(dev, M):
     assert M <= decode_max_tokens()
     c = ffn_case(M, 256, 520, seed=M, mask=edge_mask(M, "alternating")).to(dev)
