@@ -42,6 +42,10 @@ SIGNATURES = {
     "ffnk_ffn_forward": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int64,
                                  c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "ffnk_ffn_forward_train": (c_int, [c_void_p, c_int64] + [c_void_p] * 6 + [c_int64] * 4 + [c_void_p] * 9
+                               + [c_int64] * 4 + [c_void_p, c_void_p]),
+    "ffnk_ffn_backward": (c_int, [c_void_p, c_int64] + [c_void_p] * 10 + [c_int64] * 4 + [c_void_p] * 6 + [c_int64]
+                          + [c_void_p] * 6 + [c_int64] * 3 + [c_void_p, c_void_p]),
     "ffnk_read_status": (c_int, [c_void_p, c_int, c_void_p]),
     "ffnk_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
     "ffnk_set_sm_margin": (c_int, [c_int]),

@@ -41,7 +41,14 @@ constexpr int TMEM_COLS = 512;
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 enum { A_GATHER = 0, A_ROUTED = 1 };
-enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+// EPI_STORE       : out = acc
+// EPI_SWIGLU      : out = silu(gate) * up                         (accumulator = gate | up column halves)
+// EPI_SWIGLU_SAVE : same, and gate -> aux0, up -> aux1             (training forward keeps the pre-activations)
+// EPI_DSWIGLU     : acc = dH; with t1 = aux0, t3 = aux1 at the same position:
+//                   out = dH * t3 * s * (1 + t1 * (1 - s)),  aux2 = dH * t1 * s,  s = sigmoid(t1)
+//                   (the element-wise terms of the FFN backward, reference README.md:159-172)
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SWIGLU_SAVE = 2, EPI_DSWIGLU = 3 };
+__host__ __device__ constexpr bool epi_glu(int e) { return e == EPI_SWIGLU || e == EPI_SWIGLU_SAVE; }
 enum { OUT_SCATTER = 0, OUT_ROUTED = 1 };
 
 struct GemmParams {
@@ -56,6 +63,14 @@ struct GemmParams {
   int max_run_rows;     // largest tiled box used for runs of consecutive tokens (0: gather4 only)
   int* status;
   long long* prof;      // optional per-CTA wait-cycle counters (8 per CTA), see ffnk_debug_profile_buffer
+  // extra epilogue operands, addressed like `out` (same row, same leading dimension)
+  __nv_bfloat16* aux0 = nullptr;
+  __nv_bfloat16* aux1 = nullptr;
+  __nv_bfloat16* aux2 = nullptr;
+  // Optional second contraction segment (A_ROUTED + EPI_STORE only): after k_len columns of the
+  // first A matrix against the first weight, k_len1 columns of a second A matrix (tensor map
+  // m[RUN_LEVELS - 1]) against the second weight (the "1" weight maps) go into the same accumulator.
+  int k_len1 = 0;
 };
 
 // Views of one row-gathered activation matrix: m[0] fetches single rows (gather4); m[1 + i]
@@ -144,10 +159,30 @@ __device__ __forceinline__ int text_row_base(int Mv) { return ((Mv + 255) >> 8) 
 // Epilogue of one accumulator row: this thread owns TMEM lane `taddr`'s row, 256 fp32 columns.
 // EPI_STORE : out_row[n_base + c] = bf16(acc[c]),                       256 columns
 // EPI_SWIGLU: out_row[n_base + c] = bf16(silu(acc[c]) * acc[128 + c]),   128 columns
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16(f[0], f[1]);
+  o.y = pack_bf16(f[2], f[3]);
+  o.z = pack_bf16(f[4], f[5]);
+  o.w = pack_bf16(f[6], f[7]);
+  return o;
+}
+
+// Epilogue of one accumulator row: this thread owns the TMEM lane at `taddr`, BN_T fp32 columns.
+// `row_off` is the element offset of the destination row (the same in out and aux0..2).
 template <int EPI, int BN_T>
-__device__ __forceinline__ void epilogue_row(uint32_t taddr, __nv_bfloat16* out_row, bool valid, int n_base,
-                                             int n_out) {
-  if constexpr (EPI == EPI_STORE) {
+__device__ __forceinline__ void epilogue_row(uint32_t taddr, const GemmParams& p, int64_t row_off, bool valid,
+                                             int n_base) {
+  const int n_out = p.n_out;
+  if constexpr (EPI == EPI_STORE || EPI == EPI_DSWIGLU) {
 #pragma unroll 1
     for (int c = 0; c < BN_T / 32; ++c) {
       uint32_t v[32];
@@ -158,12 +193,25 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, __nv_bfloat16* out_
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (n0 + j * 8 < n_out) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
-            o.y = pack_bf16(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
-            o.z = pack_bf16(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
-            o.w = pack_bf16(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
-            *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
+            const int64_t off = row_off + n0 + j * 8;
+            float a[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = __uint_as_float(v[j * 8 + e]);
+            if constexpr (EPI == EPI_STORE) {
+              *reinterpret_cast<uint4*>(p.out + off) = pack_bf16x8(a);
+            } else {
+              float t1[8], t3[8], d1[8], d3[8];
+              unpack_bf16x8(*reinterpret_cast<const uint4*>(p.aux0 + off), t1);
+              unpack_bf16x8(*reinterpret_cast<const uint4*>(p.aux1 + off), t3);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float sg = __frcp_rn(1.0f + __expf(-t1[e]));
+                d1[e] = a[e] * t3[e] * sg * (1.0f + t1[e] * (1.0f - sg));
+                d3[e] = a[e] * t1[e] * sg;
+              }
+              *reinterpret_cast<uint4*>(p.out + off) = pack_bf16x8(d1);
+              *reinterpret_cast<uint4*>(p.aux2 + off) = pack_bf16x8(d3);
+            }
           }
         }
       }
@@ -172,7 +220,7 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, __nv_bfloat16* out_
 #pragma unroll 1
     for (int c = 0; c < BN_T / 64; ++c) {
       uint32_t g[32], u[32];
-      tmem_ld_32x32(taddr + c * 32, g);            // gate  (t1)
+      tmem_ld_32x32(taddr + c * 32, g);              // gate  (t1)
       tmem_ld_32x32(taddr + BN_T / 2 + c * 32, u);   // up    (t3)
       tmem_ld_wait();
       const int n0 = n_base + c * 32;
@@ -180,15 +228,24 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, __nv_bfloat16* out_
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (n0 + j * 8 < n_out) {
-            float h[8];
+            const int64_t off = row_off + n0 + j * 8;
+            float t1[8], t3[8], h[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) h[e] = silu_mul(__uint_as_float(g[j * 8 + e]), __uint_as_float(u[j * 8 + e]));
-            uint4 o;
-            o.x = pack_bf16(h[0], h[1]);
-            o.y = pack_bf16(h[2], h[3]);
-            o.z = pack_bf16(h[4], h[5]);
-            o.w = pack_bf16(h[6], h[7]);
-            *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = o;
+            for (int e = 0; e < 8; ++e) {
+              t1[e] = __uint_as_float(g[j * 8 + e]);
+              t3[e] = __uint_as_float(u[j * 8 + e]);
+            }
+            if constexpr (EPI == EPI_SWIGLU_SAVE) {
+              // the backward pass differentiates the bf16 values it is handed, so H is formed from those
+              const uint4 p1 = pack_bf16x8(t1), p3 = pack_bf16x8(t3);
+              *reinterpret_cast<uint4*>(p.aux0 + off) = p1;
+              *reinterpret_cast<uint4*>(p.aux1 + off) = p3;
+              unpack_bf16x8(p1, t1);
+              unpack_bf16x8(p3, t3);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) h[e] = silu_mul(t1[e], t3[e]);
+            *reinterpret_cast<uint4*>(p.out + off) = pack_bf16x8(h);
           }
         }
       }
@@ -248,10 +305,11 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
   const int Mv = p.counts[0], Mt = p.counts[1], cap = p.counts[2];
   const int tiles_v = (Mv + BM - 1) / BM;
   const int m_tiles = tiles_v + (Mt + BM - 1) / BM;
-  constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN_T / 2 : BN_T;
+  constexpr int N_PER_TILE = epi_glu(EPI) ? BN_T / 2 : BN_T;
   const int n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
   const int total_tiles = m_tiles * n_tiles;
-  const int k_steps = (p.k_len + BK - 1) / BK;
+  const int k_steps0 = (p.k_len + BK - 1) / BK;                 // first contraction segment
+  const int k_steps = k_steps0 + (p.k_len1 + BK - 1) / BK;      // plus the optional second one
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -294,27 +352,33 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
         uint8_t* sb = sa + A_BYTES;
         if (lane == 0) mbar_arrive_expect_tx(&full[stage], TSTAGE_BYTES);
         __syncwarp();
-        const int kx = ks * BK;
+        const bool seg1 = ks >= k_steps0;
+        const int kx = (seg1 ? ks - k_steps0 : ks) * BK;
         if constexpr (A_MODE == A_GATHER) {
           if (run_lanes == 0) tma_gather4(sa + lane * 512, &am.m[0], &full[stage], kx, r0, r1, r2, r3);
           else if (run_lead) tma_load_2d(sa + lane * 512, run_map, &full[stage], kx, r0);
         } else {
           if (lane == 0)
-            tma_load_2d(sa, &am.m[RUN_LEVELS], &full[stage], kx, (tc.text ? text_row_base(Mv) : 0) + tc.row0);
+            tma_load_2d(sa, &am.m[seg1 ? RUN_LEVELS - 1 : RUN_LEVELS], &full[stage], kx,
+                        (tc.text ? text_row_base(Mv) : 0) + tc.row0);
         }
         if (lane == 0) {
+          // gate/up tiles take their two column halves from two weights; plain tiles take both
+          // halves from one weight (the second weight belongs to the second contraction segment)
+          const CUtensorMap* mLo = epi_glu(EPI) ? mB0 : (seg1 ? mB1 : mB0);
+          const CUtensorMap* mHi = epi_glu(EPI) ? mB1 : mLo;
           if constexpr (!B_MN) {
-            // K-major weights: two boxes of 128 weight rows x 64 k
-            const int n0 = (EPI == EPI_SWIGLU) ? tc.nt * (BN_T / 2) : tc.nt * BN_T;
-            const int n1 = (EPI == EPI_SWIGLU) ? n0 : n0 + BN_T / 2;
-            tma_load_2d(sb, mB0, &full[stage], kx, n0);
-            tma_load_2d(sb + TB_BYTES / 2, mB1, &full[stage], kx, n1);
+            // K-major weights: two boxes of BN_T/2 weight rows x 64 k
+            const int n0 = epi_glu(EPI) ? tc.nt * (BN_T / 2) : tc.nt * BN_T;
+            const int n1 = epi_glu(EPI) ? n0 : n0 + BN_T / 2;
+            tma_load_2d(sb, mLo, &full[stage], kx, n0);
+            tma_load_2d(sb + TB_BYTES / 2, mHi, &full[stage], kx, n1);
           } else {
             // MN-major weights: four boxes of 64 k rows x 64 output columns
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const CUtensorMap* m = (EPI == EPI_SWIGLU && j >= 2) ? mB1 : mB0;
-              const int n = (EPI == EPI_SWIGLU) ? tc.nt * (BN_T / 2) + (j & 1) * 64 : tc.nt * BN_T + j * 64;
+              const CUtensorMap* m = j >= 2 ? mHi : mLo;
+              const int n = epi_glu(EPI) ? tc.nt * (BN_T / 2) + (j & 1) * 64 : tc.nt * BN_T + j * 64;
               tma_load_2d(sb + j * (TB_BYTES / 4), m, &full[stage], n, kx);
             }
           }
@@ -398,8 +462,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN_T;
-      __nv_bfloat16* out_row = p.out + dst_row * p.ldo;
-      epilogue_row<EPI, BN_T>(taddr, out_row, valid, tc.nt * (EPI == EPI_SWIGLU ? BN_T / 2 : BN_T), p.n_out);
+      epilogue_row<EPI, BN_T>(taddr, p, dst_row * p.ldo, valid, tc.nt * (epi_glu(EPI) ? BN_T / 2 : BN_T));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -485,10 +548,11 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
   const int Mv = p.counts[0], Mt = p.counts[1], cap = p.counts[2];
   const int tiles_v = (Mv + PAIR_BM - 1) / PAIR_BM;
   const int m_tiles = tiles_v + (Mt + PAIR_BM - 1) / PAIR_BM;
-  constexpr int N_PER_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  constexpr int N_PER_TILE = epi_glu(EPI) ? BN / 2 : BN;
   const int n_tiles = (p.n_out + N_PER_TILE - 1) / N_PER_TILE;
   const int total_tiles = m_tiles * n_tiles;
-  const int k_steps = (p.k_len + BK - 1) / BK;
+  const int k_steps0 = (p.k_len + BK - 1) / BK;                 // first contraction segment
+  const int k_steps = k_steps0 + (p.k_len1 + BK - 1) / BK;      // plus the optional second one
   const int text_base = text_row_base(Mv);
 
   // this CTA's 128 rows of pair tile t
@@ -535,8 +599,8 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       const bool run_lead = run_lanes > 0 && (lane & (run_lanes - 1)) == 0;
       const CUtensorMap* run_map = &am.m[run_lanes > 0 ? 32 - __clz(run_lanes) : 0];
       const bool empty_half = (A_MODE == A_GATHER) && tc.rows == 0;   // nothing to fetch: one out-of-range box
-      const CUtensorMap* mB = (EPI == EPI_SWIGLU) ? (tc.text ? (rank ? &tmBt1 : &tmBt0) : (rank ? &tmBv1 : &tmBv0))
-                                                  : (tc.text ? &tmBt0 : &tmBv0);
+      const CUtensorMap* mB0 = tc.text ? &tmBt0 : &tmBv0;
+      const CUtensorMap* mB1 = tc.text ? &tmBt1 : &tmBv1;
       for (int ks = 0; ks < k_steps; ++ks) {
         int w = 1;
         const long long tw = clock64();
@@ -553,7 +617,11 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
         const uint32_t lead_full = mapa_shared(smem_u32(&full[stage]), 0);
         if (lane == 0) mbar_arrive_expect_tx_cluster(lead_full, PAIR_STAGE_BYTES);
         __syncwarp();
-        const int kx = ks * BK;
+        const bool seg1 = ks >= k_steps0;
+        const int kx = (seg1 ? ks - k_steps0 : ks) * BK;
+        // gate/up: the leader's half of B is the gate weight, the partner's the up weight;
+        // otherwise both halves come from the segment's weight
+        const CUtensorMap* mB = epi_glu(EPI) ? (rank ? mB1 : mB0) : (seg1 ? mB1 : mB0);
         if constexpr (A_MODE == A_GATHER) {
           if (empty_half) {
             if (lane == 0) tma_load_2d_pair(sa, &am.m[RUN_LEVELS], lead_full, kx, p.pad_row);
@@ -564,11 +632,12 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
           }
         } else {
           if (lane == 0)
-            tma_load_2d_pair(sa, &am.m[RUN_LEVELS], lead_full, kx, (tc.text ? text_base : 0) + tc.row0);
+            tma_load_2d_pair(sa, &am.m[seg1 ? RUN_LEVELS - 1 : RUN_LEVELS], lead_full, kx,
+                             (tc.text ? text_base : 0) + tc.row0);
         }
         if (lane == 0) {
           // this CTA's half of the B tile
-          const int n0 = (EPI == EPI_SWIGLU) ? tc.nt * (BN / 2) : tc.nt * BN + static_cast<int>(rank) * (BN / 2);
+          const int n0 = epi_glu(EPI) ? tc.nt * (BN / 2) : tc.nt * BN + static_cast<int>(rank) * (BN / 2);
           if constexpr (!B_MN) {
             tma_load_2d_pair(sb, mB, lead_full, kx, n0);
           } else {
@@ -661,7 +730,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_row<EPI, BN>(taddr, p.out + dst_row * p.ldo, valid, tc.nt * N_PER_TILE, p.n_out);
+      epilogue_row<EPI, BN>(taddr, p, dst_row * p.ldo, valid, tc.nt * N_PER_TILE);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
@@ -704,6 +773,7 @@ struct WgradParams {
   int pad_row;
   int max_run_rows;
   int* status;
+  int routed = 0;   // 1: P and Q are in routed order (row = group base + list position), no index list
 };
 
 struct WgradTile {
@@ -784,12 +854,17 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
       const int k_steps = (wt.cnt + BK - 1) / BK;
       const int* list = p.perm + wt.list_off;
       const int4 pad4 = make_int4(p.pad_row, p.pad_row, p.pad_row, p.pad_row);
-      int4 nxt = (4 * gi < wt.cnt) ? *reinterpret_cast<const int4*>(list + 4 * gi) : pad4;
+      const int group_base = wt.text ? text_row_base(Mv) : 0;
+      int4 nxt = (!p.routed && 4 * gi < wt.cnt) ? *reinterpret_cast<const int4*>(list + 4 * gi) : pad4;
       for (int ks = 0; ks < k_steps; ++ks) {
         const int lr = ks * BK + 4 * gi;
-        const int4 v = nxt;
-        // the next k-step's rows are requested now so that the load is hidden behind this step
-        if (ks + 1 < k_steps) nxt = (lr + BK < wt.cnt) ? *reinterpret_cast<const int4*>(list + lr + BK) : pad4;
+        int4 v = nxt;
+        if (p.routed) {
+          v = make_int4(group_base + lr, group_base + lr + 1, group_base + lr + 2, group_base + lr + 3);
+        } else if (ks + 1 < k_steps) {
+          // the next k-step's rows are requested now so that the load is hidden behind this step
+          nxt = (lr + BK < wt.cnt) ? *reinterpret_cast<const int4*>(list + lr + BK) : pad4;
+        }
         int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
         const int valid = min(4, max(0, wt.cnt - lr));
         if (valid > 0) {
@@ -1034,12 +1109,12 @@ static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool 
   static const int force_pair = env_flag("FFNK_PAIR");
   static const int force_narrow = env_flag("FFNK_NARROW");
   TileChoice t{false, BN};
-  const bool pair = force_pair >= 0 ? force_pair != 0 : (M >= 4096 && a_mode == A_ROUTED && epi == EPI_STORE);
+  const bool pair = force_pair >= 0 ? force_pair != 0 : (M >= 4096 && a_mode == A_ROUTED && !epi_glu(epi));
   if (pair) {
     t.pair = true;
     return t;
   }
-  const int64_t n_per_tile = (epi == EPI_SWIGLU) ? BN / 2 : BN;
+  const int64_t n_per_tile = epi_glu(epi) ? BN / 2 : BN;
   const int64_t wide_tiles = ((M + BM - 1) / BM + 1) * ((n_out + n_per_tile - 1) / n_per_tile);
   const bool narrow = force_narrow >= 0 ? force_narrow != 0 : wide_tiles < device_info().sm_count;
   if (narrow && k_major_weights) t.bn = 64;
@@ -1053,7 +1128,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
                        int64_t M, TileChoice tile, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
-  const int n_per_tile = (EPI == EPI_SWIGLU) ? tile.bn / 2 : tile.bn;
+  const int n_per_tile = epi_glu(EPI) ? tile.bn / 2 : tile.bn;
   const int64_t n_tiles = (p.n_out + n_per_tile - 1) / n_per_tile;
   if (tile.pair) {
     int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
@@ -1091,6 +1166,28 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   if (tile.bn == 64) return go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false, 64>);
   return b_mn ? go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, true, BN>)
               : go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false, BN>);
+}
+
+// out_g[p, q] = sum over the rows of modality g of P[row, p] * Q[row, q], for both modalities.
+// rows: token rows picked through the routing lists, or (routed != 0) rows of matrices that are
+// already in routed order.  `rows_total` is the height of P and Q.
+static int launch_wgrad(const void* P, int64_t ldp, int64_t p_dim, const void* Q, int64_t ldq, int64_t q_dim,
+                        int64_t rows_total, void* out_v, void* out_t, int64_t ldo, int routed, const int32_t* perm,
+                        const int32_t* counts, int32_t* status, cudaStream_t s) {
+  const DeviceInfo& dev = device_info();
+  AMaps tmP, tmQ;
+  int r = gather_maps(tmP, P, p_dim, rows_total, ldp);
+  if (r) return r;
+  if ((r = gather_maps(tmQ, Q, q_dim, rows_total, ldq))) return r;
+  WgradParams wp{perm, counts, static_cast<__nv_bfloat16*>(out_v), static_cast<__nv_bfloat16*>(out_t), ldo,
+                 static_cast<int>(p_dim), static_cast<int>(q_dim), static_cast<int>(rows_total),
+                 max_run_rows() < 64 ? max_run_rows() : 64, status, routed};
+  int64_t grid = 2 * ((p_dim + BM - 1) / BM) * ((q_dim + BN - 1) / BN);
+  if (grid > usable_sms(dev)) grid = usable_sms(dev);
+  cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+  if (e != cudaSuccess) return cuda_status(e);
+  wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
+  return cuda_status(cudaGetLastError());
 }
 
 static bool bad_dim(int64_t v) { return v < 8 || (v & 7) || v >= (1ll << 30); }
@@ -1230,19 +1327,135 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     const void* Q = k_major ? a : g;
     const int64_t ldp = k_major ? ldg : lda, ldq = k_major ? lda : ldg;
     const int64_t p_dim = k_major ? N : K, q_dim = k_major ? K : N;
-    AMaps tmP, tmQ;
-    int r = gather_maps(tmP, P, p_dim, M, ldp);
-    if (r) return r;
-    if ((r = gather_maps(tmQ, Q, q_dim, M, ldq))) return r;
-    WgradParams wp{perm, counts, static_cast<__nv_bfloat16*>(db1), static_cast<__nv_bfloat16*>(db2),
-                   k_major ? b_stride_n : b_stride_k, static_cast<int>(p_dim), static_cast<int>(q_dim),
-                   static_cast<int>(M), max_run_rows() < 64 ? max_run_rows() : 64, status};
-    int64_t grid = 2 * ((p_dim + BM - 1) / BM) * ((q_dim + BN - 1) / BN);
-    if (grid > usable_sms(dev)) grid = usable_sms(dev);
-    cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
-    if (e != cudaSuccess) return cuda_status(e);
-    wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
-    return cuda_status(cudaGetLastError());
+    return launch_wgrad(P, ldp, p_dim, Q, ldq, q_dim, M, db1, db2, k_major ? b_stride_n : b_stride_k, 0, perm, counts,
+                        status, s);
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// MaskedFFN with a backward pass.  The reference stops at a forward kernel that would save the
+// pre-activations (_masked_ffn_fwd, ffn_kernel/ffn.py:116-221, never launched) and backward
+// kernels that do not compile (ffn_kernel/ffn.py:224-524); MaskedFFN.backward raises
+// (ffn_kernel/ops.py:34-38).  The formulas are the reference's (README.md:159-172).
+//
+// Everything between the first and the last GEMM lives in routed order:
+//   forward : xr = permute(x);  (t1, t3, hid) = gate/up(xr);  y[token] = hid @ W2
+//   backward: gr = permute(dy); (dt1, dt3) = dswiglu(gr @ W2^T; t1, t3)
+//             dW2 = gr^T hid | hid^T gr;  dW1 = dt1^T xr;  dW3 = dt3^T xr   (per modality, in storage order)
+//             dx[token] = dt1 @ W1^T + dt3 @ W3^T                          (one GEMM, two contraction segments)
+// -------------------------------------------------------------------------------------------
+extern "C" int ffnk_ffn_forward_train(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3,
+                                      const void* u1, const void* u2, const void* u3, int64_t w13_stride_k,
+                                      int64_t w13_stride_n, int64_t w2_stride_k, int64_t w2_stride_n,
+                                      const void* mask, int32_t* perm, int32_t* counts, void* scan_workspace, void* xr,
+                                      void* t1, void* t3, void* hid, void* y, int64_t ldy, int64_t M, int64_t d,
+                                      int64_t h, int32_t* status, void* stream) {
+  if (M == 0) return 0;
+  if (!x || !w1 || !w2 || !w3 || !u1 || !u2 || !u3 || !mask || !perm || !counts || !scan_workspace || !xr || !t1 ||
+      !t3 || !hid || !y)
+    return FFNK_ERR_NULL;
+  if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
+  if ((ldx & 7) || (ldy & 7) || ldx < d || ldy < d) return FFNK_ERR_ALIGN;
+  const void* al[] = {xr, t1, t3, hid, y};
+  for (const void* q : al)
+    if (reinterpret_cast<uintptr_t>(q) & 15) return FFNK_ERR_ALIGN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int r = ffnk_route(mask, M, perm, counts, scan_workspace, status, stream);
+  if (r) return r;
+  if ((r = ffnk_permute_rows(x, ldx, perm, counts, xr, d, M, d, stream))) return r;
+  const int64_t rows = ffnk_route_capacity(M) + 512;
+  {
+    AMaps tmA;
+    CUtensorMap tmB[4];
+    if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], xr, d, rows, d, BK, BM))) return r;
+    for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+    bool mn = false, mn_i = false;
+    const void* ws[4] = {w1, w3, u1, u3};
+    const TileChoice tile = pick_tile(M, h, A_ROUTED, EPI_SWIGLU_SAVE, weights_k_major(w13_stride_k, w13_stride_n, d));
+    for (int i = 0; i < 4; ++i) {
+      if ((r = weight_map(&tmB[i], WeightView{ws[i], w13_stride_k, w13_stride_n, d, h}, &mn_i, tile.bn / 2))) return r;
+      mn = mn_i;
+    }
+    GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(hid), h, static_cast<int>(h), static_cast<int>(d),
+                 static_cast<int>(rows), pick_group_m(d), max_run_rows(), status, g_prof_buffer};
+    p.aux0 = static_cast<__nv_bfloat16*>(t1);
+    p.aux1 = static_cast<__nv_bfloat16*>(t3);
+    if ((r = launch_gemm<A_ROUTED, EPI_SWIGLU_SAVE, OUT_ROUTED>(tmA, tmB, mn, p, M, tile, s))) return r;
+  }
+  return ffnk_ffn_down(hid, h, w2, u2, w2_stride_k, w2_stride_n, perm, counts, y, ldy, M, d, h, status, stream);
+}
+
+extern "C" int ffnk_ffn_backward(const void* gy, int64_t ldg, const void* xr, const void* t1, const void* t3,
+                                 const void* hid, const void* w1, const void* w2, const void* w3, const void* u1,
+                                 const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n,
+                                 int64_t w2_stride_k, int64_t w2_stride_n, const int32_t* perm, const int32_t* counts,
+                                 void* gr, void* dt1, void* dt3, void* dx, int64_t lddx, void* dw1, void* dw2,
+                                 void* dw3, void* du1, void* du2, void* du3, int64_t M, int64_t d, int64_t h,
+                                 int32_t* status, void* stream) {
+  if (M == 0) return 0;
+  if (!gy || !xr || !t1 || !t3 || !hid || !w1 || !w2 || !w3 || !u1 || !u2 || !u3 || !perm || !counts || !gr || !dt1 ||
+      !dt3 || !dx || !dw1 || !dw2 || !dw3 || !du1 || !du2 || !du3)
+    return FFNK_ERR_NULL;
+  if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
+  if ((ldg & 7) || (lddx & 7) || ldg < d || lddx < d) return FFNK_ERR_ALIGN;
+  const bool w13_k = weights_k_major(w13_stride_k, w13_stride_n, d);
+  const bool w13_n = w13_stride_n == 1 && w13_stride_k >= h;
+  const bool w2_k = weights_k_major(w2_stride_k, w2_stride_n, h);
+  const bool w2_n = w2_stride_n == 1 && w2_stride_k >= d;
+  if ((!w13_k && !w13_n) || (!w2_k && !w2_n)) return FFNK_ERR_LAYOUT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t rows = ffnk_route_capacity(M) + 512;
+  int r = ffnk_permute_rows(gy, ldg, perm, counts, gr, d, M, d, stream);
+  if (r) return r;
+
+  // (dt1, dt3) = dswiglu(gr @ W2^T): contraction over d, output columns over h
+  {
+    AMaps tmA;
+    CUtensorMap tmB[4];
+    if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], gr, d, rows, d, BK, BM))) return r;
+    for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+    bool mn1 = false, mn2 = false;
+    const TileChoice tile = pick_tile(M, h, A_ROUTED, EPI_DSWIGLU, weights_k_major(w2_stride_n, w2_stride_k, d));
+    if ((r = weight_map(&tmB[0], WeightView{w2, w2_stride_n, w2_stride_k, d, h}, &mn1, tile.bn / 2))) return r;
+    if ((r = weight_map(&tmB[2], WeightView{u2, w2_stride_n, w2_stride_k, d, h}, &mn2, tile.bn / 2))) return r;
+    tmB[1] = tmB[0];
+    tmB[3] = tmB[2];
+    GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(dt1), h, static_cast<int>(h), static_cast<int>(d),
+                 static_cast<int>(rows), pick_group_m(d), max_run_rows(), status, g_prof_buffer};
+    p.aux0 = static_cast<__nv_bfloat16*>(const_cast<void*>(t1));
+    p.aux1 = static_cast<__nv_bfloat16*>(const_cast<void*>(t3));
+    p.aux2 = static_cast<__nv_bfloat16*>(dt3);
+    if ((r = launch_gemm<A_ROUTED, EPI_DSWIGLU, OUT_ROUTED>(tmA, tmB, mn1, p, M, tile, s))) return r;
+  }
+  // weight gradients, written in each weight's storage order
+  if (w2_k) r = launch_wgrad(gr, d, d, hid, h, h, rows, dw2, du2, w2_stride_n, 1, perm, counts, status, s);   // [d][h]
+  else r = launch_wgrad(hid, h, h, gr, d, d, rows, dw2, du2, w2_stride_k, 1, perm, counts, status, s);       // [h][d]
+  if (r) return r;
+  if (w13_k) {                                                                                              // [h][d]
+    if ((r = launch_wgrad(dt1, h, h, xr, d, d, rows, dw1, du1, w13_stride_n, 1, perm, counts, status, s))) return r;
+    if ((r = launch_wgrad(dt3, h, h, xr, d, d, rows, dw3, du3, w13_stride_n, 1, perm, counts, status, s))) return r;
+  } else {                                                                                                  // [d][h]
+    if ((r = launch_wgrad(xr, d, d, dt1, h, h, rows, dw1, du1, w13_stride_k, 1, perm, counts, status, s))) return r;
+    if ((r = launch_wgrad(xr, d, d, dt3, h, h, rows, dw3, du3, w13_stride_k, 1, perm, counts, status, s))) return r;
+  }
+  // dx[token] = dt1 @ W1^T + dt3 @ W3^T: two contraction segments of length h into one accumulator
+  {
+    AMaps tmA;
+    CUtensorMap tmB[4];
+    if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], dt1, h, rows, h, BK, BM))) return r;
+    for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+    if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS - 1], dt3, h, rows, h, BK, BM))) return r;
+    bool mn = false, mn_i = false;
+    const void* ws[4] = {w1, w3, u1, u3};
+    const TileChoice tile = pick_tile(M, d, A_ROUTED, EPI_STORE, weights_k_major(w13_stride_n, w13_stride_k, h));
+    for (int i = 0; i < 4; ++i) {
+      if ((r = weight_map(&tmB[i], WeightView{ws[i], w13_stride_n, w13_stride_k, h, d}, &mn_i, tile.bn / 2))) return r;
+      mn = mn_i;
+    }
+    GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(dx), lddx, static_cast<int>(d), static_cast<int>(h),
+                 static_cast<int>(rows), pick_group_m(2 * h), max_run_rows(), status, g_prof_buffer};
+    p.k_len1 = static_cast<int>(h);
+    return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn, p, M, tile, s);
   }
 }
 

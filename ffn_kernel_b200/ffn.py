@@ -132,3 +132,68 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
         _phase("end")
     maybe_check(dev)
     return y
+
+
+def _bf16_ffn_train_forward(x, w1, w2, w3, u1, u2, u3, mask):
+    """Forward pass that keeps the routed activations for the backward pass.
+    Returns ``(y, saved)``; ``saved`` goes to ``_bf16_ffn_backward`` unchanged."""
+    x = _activation(x, "x")
+    M, d = x.shape
+    h = w1.shape[1] if isinstance(w1, torch.Tensor) and w1.dim() == 2 else -1
+    w1, w3, u1, u3 = _weights((w1, w3, u1, u3), ("w1", "w3", "u1", "u3"), d, h)
+    w2, u2 = _weights((w2, u2), ("w2", "u2"), h, d)
+    _check_dims(d=d, h=h)
+    dev = x.device
+    if not isinstance(mask, torch.Tensor) or mask.dim() != 1 or mask.shape[0] != M or mask.device != dev:
+        raise RuntimeError(f"mask must have shape [{M}] on {dev}")
+    if mask.dtype not in (torch.bool, torch.uint8):
+        raise RuntimeError(f"mask must be torch.bool (or uint8), got {mask.dtype}")
+    L = lib()
+    with torch.cuda.device(dev):
+        y = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
+        cap = int(L.ffnk_route_capacity(M))
+        rows = cap + 512
+        perm = torch.empty(max(2 * cap, 4), dtype=torch.int32, device=dev)
+        counts = torch.empty(4, dtype=torch.int32, device=dev)
+        xr = torch.empty((rows, d), device=dev, dtype=torch.bfloat16)
+        t1, t3, hid = (torch.empty((rows, h), device=dev, dtype=torch.bfloat16) for _ in range(3))
+        saved = dict(M=M, d=d, h=h, perm=perm, counts=counts, xr=xr, t1=t1, t3=t3, hid=hid,
+                     weights=(w1, w2, w3, u1, u2, u3))
+        if M == 0:
+            return y, saved
+        scan = torch.empty(max(int(L.ffnk_route_workspace_bytes(M)), 4), dtype=torch.uint8, device=dev)
+        check("ffnk_ffn_forward_train", L.ffnk_ffn_forward_train(
+            x.data_ptr(), x.stride(0), w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), u1.data_ptr(), u2.data_ptr(),
+            u3.data_ptr(), w1.stride(0), w1.stride(1), w2.stride(0), w2.stride(1), mask.contiguous().data_ptr(),
+            perm.data_ptr(), counts.data_ptr(), scan.data_ptr(), xr.data_ptr(), t1.data_ptr(), t3.data_ptr(),
+            hid.data_ptr(), y.data_ptr(), y.stride(0), M, d, h, status_word(dev).data_ptr(), stream_ptr(dev)))
+    maybe_check(dev)
+    return y, saved
+
+
+def _bf16_ffn_backward(gy, saved):
+    """Gradients ``(dx, dw1, dw2, dw3, du1, du2, du3)``; weight gradients carry their weights' strides."""
+    M, d, h = saved["M"], saved["d"], saved["h"]
+    w1, w2, w3, u1, u2, u3 = saved["weights"]
+    dev = saved["xr"].device
+    if tuple(gy.shape) != (M, d):
+        raise RuntimeError(f"grad must have shape [{M}, {d}], got {tuple(gy.shape)}")
+    gy = _activation(gy, "grad")
+    L = lib()
+    with torch.cuda.device(dev):
+        dx = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
+        grads = [torch.empty_strided(w.shape, w.stride(), device=dev, dtype=torch.bfloat16)
+                 for w in (w1, w2, w3, u1, u2, u3)]
+        if M == 0:
+            return (dx, *[g.zero_() for g in grads])
+        rows = saved["xr"].shape[0]
+        gr = torch.empty((rows, d), device=dev, dtype=torch.bfloat16)
+        dt1, dt3 = (torch.empty((rows, h), device=dev, dtype=torch.bfloat16) for _ in range(2))
+        check("ffnk_ffn_backward", L.ffnk_ffn_backward(
+            gy.data_ptr(), gy.stride(0), saved["xr"].data_ptr(), saved["t1"].data_ptr(), saved["t3"].data_ptr(),
+            saved["hid"].data_ptr(), w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), u1.data_ptr(), u2.data_ptr(),
+            u3.data_ptr(), w1.stride(0), w1.stride(1), w2.stride(0), w2.stride(1), saved["perm"].data_ptr(),
+            saved["counts"].data_ptr(), gr.data_ptr(), dt1.data_ptr(), dt3.data_ptr(), dx.data_ptr(), dx.stride(0),
+            *[g.data_ptr() for g in grads], M, d, h, status_word(dev).data_ptr(), stream_ptr(dev)))
+    maybe_check(dev)
+    return (dx, *grads)

@@ -2,8 +2,8 @@
 
 Drop-in for ``ffn_kernel/ops.py:9-38``: same ``torch.autograd.Function`` classes, same
 argument order and tensor layouts, same gradients returned
-(``(da, db1, db2, None)``, ``ffn_kernel/ops.py:24``), and ``MaskedFFN.backward`` raises
-``NotImplementedError`` exactly as the reference does (``ffn_kernel/ops.py:34-38``).
+(``(da, db1, db2, None)``, ``ffn_kernel/ops.py:24``).  One extension: ``MaskedFFN.backward``, which
+the reference leaves raising ``NotImplementedError`` (``ffn_kernel/ops.py:34-38``), is implemented.
 """
 from __future__ import annotations
 
@@ -11,7 +11,8 @@ from torch.amp import custom_bwd, custom_fwd
 from torch.autograd import Function
 from torch.autograd.function import once_differentiable
 
-from .ffn import _bf16_ffn_forward, _bf16_ffn_fused_forward  # noqa: F401  (re-exported)
+from .ffn import (_bf16_ffn_backward, _bf16_ffn_forward, _bf16_ffn_fused_forward,  # noqa: F401  (re-exported)
+                  _bf16_ffn_train_forward)
 from .linear import _bf16_linear_backward, _bf16_linear_forward
 from .route import route
 
@@ -41,15 +42,28 @@ class MaskedLinear(Function):
 
 
 class MaskedFFN(Function):
-    """``MaskedFFN.apply(a, w1, w2, w3, u1, u2, u3, mask)``: routed SwiGLU FFN, forward only."""
+    """``MaskedFFN.apply(a, w1, w2, w3, u1, u2, u3, mask)``: routed SwiGLU FFN.
+
+    The forward pass is the reference's (``ffn_kernel/ops.py:28-32``).  The reference's backward
+    raises ``NotImplementedError`` (``ffn_kernel/ops.py:34-38``, its kernels are unfinished); here
+    it is implemented after the reference's own formulas (``README.md:159-172``): when any input
+    requires a gradient, the forward keeps the routed activations and pre-activations."""
 
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, a, w1, w2, w3, u1, u2, u3, mask):
+        if any(ctx.needs_input_grad[:7]):
+            y, ctx.saved = _bf16_ffn_train_forward(a, w1, w2, w3, u1, u2, u3, mask)
+            return y
+        ctx.saved = None
         return _bf16_ffn_fused_forward(a, w1, w2, w3, u1, u2, u3, mask)
 
     @staticmethod
     @once_differentiable
     @custom_bwd(device_type="cuda")
     def backward(ctx, grad):
-        raise NotImplementedError
+        if ctx.saved is None:
+            raise RuntimeError("MaskedFFN.backward called but the forward pass saw no input that requires grad")
+        grads = _bf16_ffn_backward(grad, ctx.saved)
+        ctx.saved = None
+        return (*grads, None)

@@ -144,6 +144,17 @@ def main():
         t = timeit(lambda: _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False), a.iters, a.warmup)
         emit(kernel="ffn_forward(Python API, one library call)", M=M, d=d, h=h, mask=a.mask, ms=t,
              tflops=6 * M * d * h / t / 1e9, weight_gbs=6 * d * h * 2 / t / 1e6)
+        if a.bwd:
+            from .ffn import _bf16_ffn_backward, _bf16_ffn_train_forward
+            gy = torch.randn(M, d, device=dev, dtype=torch.bfloat16)
+            t = timeit(lambda: _bf16_ffn_train_forward(*c.apply_args()), a.iters, a.warmup)
+            emit(kernel="ffn_forward_train(saves t1, t3, hid)", M=M, d=d, h=h, mask=a.mask, ms=t,
+                 tflops=6 * M * d * h / t / 1e9)
+            _, saved = _bf16_ffn_train_forward(*c.apply_args())
+            t = timeit(lambda: _bf16_ffn_backward(gy, saved), max(3, a.iters // 2), a.warmup)
+            emit(kernel="ffn_backward(dx + six dW)", M=M, d=d, h=h, mask=a.mask, ms=t,
+                 tflops=12 * M * d * h / t / 1e9)
+            del saved
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)

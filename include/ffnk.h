@@ -169,6 +169,32 @@ int ffnk_ffn_forward(const void* x, int64_t ldx, const void* w1, const void* w2,
                      int64_t w2_stride_n, const void* mask, void* workspace, int64_t workspace_bytes, void* y,
                      int64_t ldy, int64_t M, int64_t d, int64_t h, int allow_decode, int32_t* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * MaskedFFN forward that keeps what the backward pass needs, and the backward pass.  The
+ * reference has no working counterpart: its saving forward kernel (_masked_ffn_fwd,
+ * ffn_kernel/ffn.py:116-221) is never launched, its backward kernels (ffn_kernel/ffn.py:224-524)
+ * do not compile and MaskedFFN.backward raises (ffn_kernel/ops.py:34-38); the formulas are those
+ * of the reference's README.md:159-172.
+ *
+ * rows = ffnk_route_capacity(M) + 512.  The caller owns, and keeps alive between the two calls:
+ *   perm int32[2*cap], counts int32[4]      routing lists (written by the forward)
+ *   xr  bf16 [rows, d]                      x in routed order
+ *   t1, t3, hid bf16 [rows, h]              gate and up pre-activations, and silu(t1) * t3
+ * Backward scratch: gr bf16 [rows, d], dt1 and dt3 bf16 [rows, h].  The six weight gradients are
+ * written with the strides of their weights; dx is [M, d] in token order.
+ * ------------------------------------------------------------------------------------- */
+int ffnk_ffn_forward_train(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
+                           const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n,
+                           int64_t w2_stride_k, int64_t w2_stride_n, const void* mask, int32_t* perm, int32_t* counts,
+                           void* scan_workspace, void* xr, void* t1, void* t3, void* hid, void* y, int64_t ldy,
+                           int64_t M, int64_t d, int64_t h, int32_t* status, void* stream);
+int ffnk_ffn_backward(const void* gy, int64_t ldg, const void* xr, const void* t1, const void* t3, const void* hid,
+                      const void* w1, const void* w2, const void* w3, const void* u1, const void* u2, const void* u3,
+                      int64_t w13_stride_k, int64_t w13_stride_n, int64_t w2_stride_k, int64_t w2_stride_n,
+                      const int32_t* perm, const int32_t* counts, void* gr, void* dt1, void* dt3, void* dx,
+                      int64_t lddx, void* dw1, void* dw2, void* dw3, void* du1, void* du2, void* du3, int64_t M,
+                      int64_t d, int64_t h, int32_t* status, void* stream);
+
 /* Synchronises `stream`, copies the status word to the host and returns it (0 = ok, >0 one of
  * the device status codes, <0 an error as above).  If `clear` is non-zero the word is reset to 0. */
 int ffnk_read_status(int32_t* status, int clear, void* stream);

@@ -20,6 +20,8 @@ What is restated, with the reference lines each function follows:
   ``dB1 = A[m]^T G[m]``, ``dB2 = A[~m]^T G[~m]``.
 * ``masked_ffn``               -- ``test_ffn.py:32-47``:
   ``w2(silu(w1 x) * w3 x) * m + u2(silu(u1 x) * u3 x) * ~m``.
+* ``masked_ffn_backward``      -- autograd through the same expression; the reference states the
+  closed form in ``README.md:159-172`` but ships no working kernel for it.
 * ``routing``                  -- the compacted per-modality row lists that
   replace the reference's per-tile uniformity test
   (``ffn_kernel/linear.py:132,137``): ``nonzero(mask)`` / ``nonzero(~mask)``.
@@ -85,6 +87,20 @@ def masked_ffn(x, w1, w2, w3, u1, u2, u3, mask, dtype=torch.float32) -> torch.Te
     pv = torch.nn.functional.silu(x @ w1.to(dtype)) * (x @ w3.to(dtype))
     pt = torch.nn.functional.silu(x @ u1.to(dtype)) * (x @ u3.to(dtype))
     return (pv @ w2.to(dtype)) * mv + (pt @ u2.to(dtype)) * mt
+
+
+def masked_ffn_backward(g, x, w1, w2, w3, u1, u2, u3, mask, dtype=torch.float32):
+    """Gradients of ``masked_ffn`` for upstream gradient g [M,d], by autograd through the same
+    dense-then-select expression as the reference module (``test_ffn.py:41-47``; closed form in
+    the reference's ``README.md:159-172``).  Returns (dx, dw1, dw2, dw3, du1, du2, du3), weight
+    gradients in the operator's [in, out] orientation."""
+    leaves = [t.detach().to(dtype).clone().requires_grad_(True) for t in (x, w1, w2, w3, u1, u2, u3)]
+    xx, a1, a2, a3, b1, b2, b3 = leaves
+    mv, mt = _sel(mask, dtype)
+    pv = torch.nn.functional.silu(xx @ a1) * (xx @ a3)
+    pt = torch.nn.functional.silu(xx @ b1) * (xx @ b3)
+    y = (pv @ a2) * mv + (pt @ b2) * mt
+    return torch.autograd.grad(y, leaves, g.to(dtype))
 
 
 def max_rel_err(y, ref) -> float:

@@ -80,7 +80,7 @@ def linear_case(TorchLinear, name, B, S, K, N, seed):
                         mask=mask.numpy(), **out)
 
 
-def ffn_case(TorchFFN, name, B, S, d, h, seed):
+def ffn_case(TorchFFN, name, B, S, d, h, seed, with_grads=False):
     gen = torch.Generator().manual_seed(seed)
     x = _bf16((B, S, d), 1.0, gen)
     names = ("w1", "w2", "w3", "u1", "u2", "u3")
@@ -95,6 +95,22 @@ def ffn_case(TorchFFN, name, B, S, d, h, seed):
                 getattr(mod, n).weight.copy_(ws[n].to(dt))
         y = mod(x.to(dt), mask)
         out[f"y_{tag}"] = y.float().numpy() if dt == torch.float32 else _u16(y)
+    if with_grads:
+        # The reference module's forward is wrapped in torch.no_grad(); the undecorated function
+        # (``__wrapped__``) is the same expression and lets autograd produce the FFN gradients the
+        # reference itself never implemented (ffn_kernel/ops.py:34-38).  float32, [out, in] storage order.
+        g = _bf16((B, S, d), 1.0, gen)
+        mod = TorchFFN(d, h).float()
+        with torch.no_grad():
+            for n in names:
+                getattr(mod, n).weight.copy_(ws[n].float())
+        xi = x.float().requires_grad_(True)
+        y = TorchFFN.forward.__wrapped__(mod, xi, mask)
+        y.backward(g.float())
+        out["g"] = _u16(g)
+        out["dx_f32"] = xi.grad.numpy()
+        for n in names:
+            out[f"d{n}_f32"] = getattr(mod, n).weight.grad.numpy()
     np.savez_compressed(os.path.join(HERE, name + ".npz"), x=_u16(x), mask=mask.numpy(),
                         **{n: _u16(w) for n, w in ws.items()}, **out)
 
@@ -104,6 +120,6 @@ if __name__ == "__main__":
     TorchLinear, TorchFFN = _import_reference(ref)
     linear_case(TorchLinear, "linear_b2_s192_k64_n96", 2, 192, 64, 96, seed=1)
     linear_case(TorchLinear, "linear_b1_s200_k128_n192", 1, 200, 128, 192, seed=2)
-    ffn_case(TorchFFN, "ffn_b2_s160_d64_h160", 2, 160, 64, 160, seed=3)
+    ffn_case(TorchFFN, "ffn_b2_s160_d64_h160", 2, 160, 64, 160, seed=3, with_grads=True)
     ffn_case(TorchFFN, "ffn_b1_s257_d128_h256", 1, 257, 128, 256, seed=4)
     print("golden vectors written to", HERE)

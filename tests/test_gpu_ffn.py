@@ -112,13 +112,75 @@ def test_tensor_parallel_slices_of_the_weight_views(dev):
     assert O.max_rel_err(acc, ref) < TOL
 
 
-def test_backward_raises_like_the_reference(dev):
-    # ffn_kernel/ops.py:34-38
+def _ffn_grads(g, layout="T"):
+    """Run MaskedFFN forward + backward on the GPU case g; returns (y, dx, [dw in operator orientation])."""
+    x = g.x.clone().requires_grad_(True)
+    if layout == "T":       # leaves are the nn.Linear storages, the operator sees their .T views
+        leaves = [w.clone().requires_grad_(True) for w in (g.w1, g.w2, g.w3, g.u1, g.u2, g.u3)]
+        views = [w.T for w in leaves]
+    else:                   # contiguous [in, out] leaves
+        leaves = [w.T.contiguous().requires_grad_(True) for w in (g.w1, g.w2, g.w3, g.u1, g.u2, g.u3)]
+        views = leaves
+    y = MaskedFFN.apply(x, *views, g.mask)
+    return x, leaves, y
+
+
+@pytest.mark.parametrize("M,d,h", [(1, 64, 64), (9, 64, 160), (300, 128, 328), (1000, 256, 520), (4099, 256, 512)])
+@pytest.mark.parametrize("layout", ["T", "C"])
+@pytest.mark.parametrize("kind", ["bernoulli", "span", "all_visual", "all_text"])
+def test_backward_parity(dev, M, d, h, layout, kind):
+    # the reference leaves MaskedFFN.backward unimplemented (ffn_kernel/ops.py:34-38); the oracle
+    # differentiates the reference module's expression (formulas: reference README.md:159-172)
+    c = ffn_case(M, d, h, seed=M + h, mask=edge_mask(M, kind, seed=d))
+    gy = (torch.randn(M, d, generator=torch.Generator().manual_seed(7))).to(torch.bfloat16)
+    ref = O.masked_ffn_backward(gy, *c.apply_args())
+    x, leaves, y = _ffn_grads(c.to(dev), layout)
+    y.backward(gy.to(dev))
+    check_status()
+    assert O.max_rel_err(y, O.masked_ffn(*c.apply_args())) < TOL
+    assert O.max_rel_err(x.grad, ref[0]) < TOL
+    for leaf, r, name in zip(leaves, ref[1:], ("w1", "w2", "w3", "u1", "u2", "u3")):
+        got = leaf.grad.T if layout == "T" else leaf.grad
+        assert got.shape == r.shape
+        assert O.max_rel_err(got, r) < TOL, name
+
+
+def test_backward_golden(dev):
+    z = load_golden(FFN_GOLDEN[0])
+    names = ("w1", "w2", "w3", "u1", "u2", "u3")
+    x = z["x"].flatten(0, 1).to(dev).requires_grad_(True)
+    leaves = [z[n].to(dev).requires_grad_(True) for n in names]
+    y = MaskedFFN.apply(x, *(w.T for w in leaves), z["mask"].flatten().to(dev))
+    y.backward(z["g"].flatten(0, 1).to(dev))
+    check_status()
+    assert O.max_rel_err(x.grad, z["dx_f32"].flatten(0, 1)) < TOL
+    for leaf, n in zip(leaves, names):
+        assert O.max_rel_err(leaf.grad, z[f"d{n}_f32"]) < TOL, n
+
+
+def test_backward_only_when_asked_for(dev):
     c = ffn_case(64, 64, 64, seed=1).to(dev)
-    x = c.x.clone().requires_grad_(True)
-    y = MaskedFFN.apply(x, *c.apply_args()[1:])
-    with pytest.raises(NotImplementedError):
-        y.sum().backward()
+    y = MaskedFFN.apply(*c.apply_args())            # nothing requires grad: inference path
+    assert not y.requires_grad
+
+
+def test_backward_full_size_rows_sampled(dev):
+    # d = 1024 / h = 2048, M = 32768: dx on sampled rows (row independence) and a column block of dW
+    M, d, h = 32768, 1024, 2048
+    c = ffn_case(M, d, h, seed=0)
+    gy = torch.randn(M, d, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    x, leaves, y = _ffn_grads(c.to(dev), "T")
+    y.backward(gy.to(dev))
+    check_status()
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:96]
+    ref = O.masked_ffn_backward(gy[rows], c.x[rows], *c.apply_args()[1:7], c.mask[rows])
+    assert O.max_rel_err(x.grad[rows.to(dev)], ref[0]) < TOL
+    assert all(bool(torch.isfinite(l.grad.float()).all()) for l in leaves)
+    # dW2 (visual) = H_v^T G_v: check against the oracle's intermediate on all rows, fp32 on CPU
+    hv = O.masked_ffn_gateup(c.x, c.w1.T, c.w3.T, c.u1.T, c.u3.T, c.mask)
+    mv = c.mask.view(-1, 1).float()
+    dw2_ref = (hv * mv).T @ gy.float()              # [h, d]
+    assert O.max_rel_err(leaves[1].grad.T, dw2_ref) < TOL
 
 
 def test_empty_input(dev):

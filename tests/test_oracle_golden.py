@@ -50,6 +50,16 @@ def test_ffn_bf16_reference_run_is_within_stated_tolerance_of_fp32(name):
     assert O.max_rel_err(z["y_bf16"].float(), z["y_f32"]) < 1e-2
 
 
+def test_ffn_backward_fp32_matches_reference_autograd():
+    z = load_golden(FFN_GOLDEN[0])
+    x, g, mask = z["x"].flatten(0, 1), z["g"].flatten(0, 1), z["mask"].flatten()
+    names = ("w1", "w2", "w3", "u1", "u2", "u3")
+    grads = O.masked_ffn_backward(g, x, *(z[n].T for n in names), mask)
+    assert O.max_rel_err(grads[0], z["dx_f32"].flatten(0, 1)) < 1e-5
+    for gr, n in zip(grads[1:], names):
+        assert O.max_rel_err(gr.T, z[f"d{n}_f32"]) < 1e-5, n       # golden gradients are in [out, in] storage order
+
+
 def test_ffn_composes_gateup_and_linear():
     z = load_golden(FFN_GOLDEN[0])
     x, mask = z["x"].flatten(0, 1), z["mask"].flatten()
