@@ -113,3 +113,42 @@ def masked_linear_dp(a, b1, b2, mask, rank: int, world: int, linear_fn: Callable
         linear_fn = MaskedLinear.apply
     rows = row_shard(a.shape[0], rank, world)
     return rows, linear_fn(a[rows], b1, b2, mask[rows])
+
+
+def all_reduce_gradients(tensors: Sequence[torch.Tensor], group=None, bucket_bytes: int = 256 << 20,
+                         average: bool = False) -> None:
+    """Data-parallel training: sum (or average) the per-rank weight gradients in place.
+
+    In token-sharded mode every rank's ``MaskedLinear`` / ``MaskedFFN`` backward yields the partial
+    weight gradient of its own tokens (the reference has no distributed path; its
+    ``_bf16_linear_backward``, ``ffn_kernel/linear.py:455-496``, is the single-device partial).
+    Gradients are packed into flat fp32 buckets so that a few large NCCL all-reduces run instead
+    of one per tensor, and the sum over ranks is taken in fp32."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    world = dist.get_world_size(group)
+    bucket, size = [], 0
+
+    def flush():
+        nonlocal bucket, size
+        if not bucket:
+            return
+        flat = torch.cat([t.reshape(-1).float() for t in bucket])
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        if average:
+            flat /= world
+        off = 0
+        for t in bucket:
+            n = t.numel()
+            t.copy_(flat[off:off + n].view(t.shape))       # copy_ honours the (possibly transposed) strides
+            off += n
+        bucket, size = [], 0
+
+    for t in tensors:
+        if t is None:
+            continue
+        bucket.append(t)
+        size += t.numel() * 4
+        if size >= bucket_bytes:
+            flush()
+    flush()

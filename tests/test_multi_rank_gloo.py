@@ -47,8 +47,16 @@ def _worker(rank, world, port, chunks, out):
             refused = False
         except ValueError:
             refused = True
+        # data-parallel gradient sum: each rank's partial dW over its own rows adds up to the full dW
+        lg = linear_case(200, 32, 40, seed=7, with_grad=True)
+        rr = tp.row_shard(200, rank, world)
+        _, d1, d2 = O.masked_linear_backward(lg.g[rr], lg.x[rr], lg.wv.T, lg.wt.T, lg.mask[rr])
+        d1 = d1.T.contiguous().T                                # a transposed-stride gradient, like weight.T views
+        tp.all_reduce_gradients([d1, None, d2], bucket_bytes=1024)
+        _, f1, f2 = O.masked_linear_backward(lg.g, lg.x, lg.wv.T, lg.wt.T, lg.mask)
+        err_grad = max(O.max_rel_err(d1, f1), O.max_rel_err(d2, f2))
         if rank == 0:
-            out.put((err_tp, err_dp, counts, refused))
+            out.put((err_tp, err_dp, counts, refused, err_grad))
     finally:
         dist.destroy_process_group()
 
@@ -64,8 +72,8 @@ def test_tp_and_dp_two_ranks(chunks):
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
-    err_tp, err_dp, counts, refused = q.get()
-    assert refused
+    err_tp, err_dp, counts, refused, err_grad = q.get()
+    assert refused and err_grad < 1e-5
     assert err_tp < 5e-3 and err_dp < 1e-6          # y is returned in bf16 (one rounding)
     assert counts == [(0, 151), (151, 301)]          # contiguous, disjoint, covering
 
