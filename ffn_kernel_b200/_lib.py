@@ -10,7 +10,8 @@ import os
 from ctypes import c_char_p, c_int, c_int32, c_int64, c_void_p, POINTER
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libffnk.so")
+# FFNK_LIB points at another build of the same library (A/B runs of kernel variants)
+LIB_PATH = os.environ.get("FFNK_LIB") or os.path.join(_HERE, "lib", "libffnk.so")
 
 _I32P = POINTER(c_int32)
 

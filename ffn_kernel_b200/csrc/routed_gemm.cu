@@ -7,14 +7,14 @@
 // both modalities, computes both products and selects (ffn_kernel/linear.py:142-149,
 // ffn_kernel/ffn.py:86-99).
 //
-// Structure of one persistent CTA (192 threads, one CTA per SM):
+// Structure of one persistent CTA (192 or 320 threads, one CTA per SM):
 //   warp 0      producer: TMA.  A rows are fetched with gather4 (four arbitrary rows of 128 B
 //               per instruction, lane l of the warp owns rows 4l..4l+3 of the tile) or, when A
 //               is already in routed order, with one tiled load.  B comes from the weight's own
 //               storage, K-major ([N,K], the nn.Linear.weight.T view) or MN-major ([K,N]).
 //   warp 1      issues tcgen05.mma (bf16 x bf16 -> fp32 in TMEM), 128x256x16 per instruction,
 //               four per 64-wide k-step; owns the TMEM allocation.
-//   warps 2..5  epilogue: tcgen05.ld the accumulator, convert (optionally SiLU(t1)*t3), store
+//   warps 2..5 (or 2..9 when tiles are short in K: two warps per TMEM lane quarter)  epilogue: tcgen05.ld the accumulator, convert (optionally SiLU(t1)*t3), store
 //               bf16 rows to their destination (token order via the list, or routed order).
 // Shared-memory stages are handed between producer and MMA with full/empty mbarriers; the
 // accumulator is double buffered in TMEM (2 x 256 columns) so the epilogue of tile i runs
@@ -36,7 +36,21 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;    // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;    // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+// The epilogue has one or two warps per TMEM lane quarter (each drains all, or half, of the columns);
+// the launch picks 192 or 320 threads: the second set pays off only when tiles are short in K and the
+// epilogue would otherwise hold up the MMA issuer (measured: K=1024 gate/up +23 %, K=11008 down -6 %).
+constexpr int GEMM_THREADS_MAX = 320;
 constexpr int GEMM_THREADS = 192;
+__device__ __forceinline__ int epilogue_parts() { return (static_cast<int>(blockDim.x) - 64) >> 7; }
+static int gemm_threads_for(int64_t k_len_total) {
+  static const int forced = [] {   // FFNK_EPI_WARPS=4/8 overrides the choice for experiments
+    const char* e = getenv("FFNK_EPI_WARPS");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 4) return GEMM_THREADS;
+  if (forced == 8) return GEMM_THREADS_MAX;
+  return k_len_total <= 2048 ? GEMM_THREADS_MAX : GEMM_THREADS;
+}
 constexpr int TMEM_COLS = 512;
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
@@ -180,11 +194,13 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
 // `row_off` is the element offset of the destination row (the same in out and aux0..2).
 template <int EPI, int BN_T>
 __device__ __forceinline__ void epilogue_row(uint32_t taddr, const GemmParams& p, int64_t row_off, bool valid,
-                                             int n_base) {
+                                             int n_base, int part, int parts) {
+  // this warp drains chunk range [part * CH / parts, (part + 1) * CH / parts) of the tile's columns
   const int n_out = p.n_out;
   if constexpr (EPI == EPI_STORE || EPI == EPI_DSWIGLU) {
+    constexpr int CH = BN_T / 32;
 #pragma unroll 1
-    for (int c = 0; c < BN_T / 32; ++c) {
+    for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
       uint32_t v[32];
       tmem_ld_32x32(taddr + c * 32, v);
       tmem_ld_wait();
@@ -217,8 +233,9 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, const GemmParams& p
       }
     }
   } else {
+    constexpr int CH = BN_T / 64;
 #pragma unroll 1
-    for (int c = 0; c < BN_T / 64; ++c) {
+    for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
       uint32_t g[32], u[32];
       tmem_ld_32x32(taddr + c * 32, g);              // gate  (t1)
       tmem_ld_32x32(taddr + BN_T / 2 + c * 32, u);   // up    (t3)
@@ -256,7 +273,7 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, const GemmParams& p
 // BN_T = 256 is the throughput tile; BN_T = 64 (K-major weights only) spreads a problem with few row
 // tiles over more SMs: 8 stages of 24 KiB, four times as many column tiles.
 template <int A_MODE, int EPI, int OUT_MODE, bool B_MN, int BN_T>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_MAX, 1)
 routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUtensorMap tmBv0,
                    const __grid_constant__ CUtensorMap tmBv1, const __grid_constant__ CUtensorMap tmBt0,
                    const __grid_constant__ CUtensorMap tmBt1, const GemmParams p) {
@@ -283,7 +300,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 4);
+      mbar_init(&tempty[i], 4 * epilogue_parts());
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -441,6 +458,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int part = (warp - 2) >> 2;    // which half of the columns it drains
     const int row = q * 32 + lane;       // row of the tile held by this thread
     int it = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
@@ -462,7 +480,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN_T;
-      epilogue_row<EPI, BN_T>(taddr, p, dst_row * p.ldo, valid, tc.nt * (epi_glu(EPI) ? BN_T / 2 : BN_T));
+      epilogue_row<EPI, BN_T>(taddr, p, dst_row * p.ldo, valid, tc.nt * (epi_glu(EPI) ? BN_T / 2 : BN_T), part, epilogue_parts());
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -499,7 +517,7 @@ constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 constexpr int PAIR_BM = 2 * BM;                                 // 256 tile rows per pair
 
 template <int A_MODE, int EPI, int OUT_MODE, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_MAX, 1)
 routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUtensorMap tmBv0,
                         const __grid_constant__ CUtensorMap tmBv1, const __grid_constant__ CUtensorMap tmBt0,
                         const __grid_constant__ CUtensorMap tmBt1, const GemmParams p) {
@@ -525,7 +543,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);     // the leader's commit, delivered to both CTAs
-      mbar_init(&tempty[i], 8);    // four epilogue warps of each CTA (used in the leader only)
+      mbar_init(&tempty[i], 8 * epilogue_parts());   // the epilogue warps of both CTAs (used in the leader only)
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -706,6 +724,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
+    const int part = (warp - 2) >> 2;
     const int row = q * 32 + lane;
     int it = 0;
     long long t_begin = clock64(), t_wait = 0;
@@ -730,7 +749,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_row<EPI, BN>(taddr, p, dst_row * p.ldo, valid, tc.nt * N_PER_TILE);
+      epilogue_row<EPI, BN>(taddr, p, dst_row * p.ldo, valid, tc.nt * N_PER_TILE, part, epilogue_parts());
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
@@ -796,7 +815,7 @@ __device__ __forceinline__ WgradTile decode_wgrad_tile(int t, int p_tiles, int q
   return w;
 }
 
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_MAX, 1)
 wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm, const WgradParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -817,7 +836,7 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 4);
+      mbar_init(&tempty[i], 4 * epilogue_parts());
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -963,6 +982,7 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;
+    const int part = (warp - 2) >> 2;
     const int row = q * 32 + lane;
     int it = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
@@ -974,7 +994,7 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
       if (wt.cnt == 0) {
         // a modality without tokens has a zero gradient
         if (valid) {
-          for (int c = 0; c < BN; c += 8)
+          for (int c = part * (BN / epilogue_parts()); c < (part + 1) * (BN / epilogue_parts()); c += 8)
             if (q_base + c < p.q_dim) *reinterpret_cast<uint4*>(out_row + q_base + c) = make_uint4(0, 0, 0, 0);
         }
         continue;
@@ -992,7 +1012,7 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = part * (BN / 32) / epilogue_parts(); c < (part + 1) * (BN / 32) / epilogue_parts(); ++c) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + c * 32, v);
         tmem_ld_wait();
@@ -1139,7 +1159,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
       if (e != cudaSuccess) return cuda_status(e);
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-      cfg.blockDim = dim3(GEMM_THREADS);
+      cfg.blockDim = dim3(gemm_threads_for(static_cast<int64_t>(p.k_len) + p.k_len1));
       cfg.dynamicSmemBytes = PAIR_SMEM;
       cfg.stream = stream;
       cudaLaunchAttribute attr[1];
@@ -1160,7 +1180,8 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   auto go = [&](auto kernel) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return cuda_status(e);
-    kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
+    kernel<<<static_cast<unsigned>(grid), gemm_threads_for(static_cast<int64_t>(p.k_len) + p.k_len1), GEMM_SMEM, stream>>>(
+        tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
     return cuda_status(cudaGetLastError());
   };
   if (tile.bn == 64) return go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false, 64>);
