@@ -9,8 +9,8 @@
 //   counts[0] = Mv, counts[1] = Mt, counts[2] = cap, counts[3] = M
 //
 // Integer work, bit-exact with nonzero(mask) / nonzero(~mask).  One pass over the mask: a
-// chained scan with decoupled look-back.  Tiles are handed out by an atomic ticket so that a
-// tile's predecessors have always started; the look-back spin is bounded all the same.
+// chained scan with decoupled look-back over tiles in block-index order; the look-back spin is
+// bounded, so a tile whose predecessor never publishes reports a status code instead of hanging.
 //
 // Algorithmic traffic: 1 byte read + 4 bytes written per token.
 #include <mutex>
@@ -21,8 +21,9 @@
 namespace ffnk {
 
 constexpr int kRouteThreads = 256;
-constexpr int kRoutePerThread = 16;                             // one 128-bit load of mask bytes
-constexpr int kRouteTile = kRouteThreads * kRoutePerThread;     // 4096 tokens per tile
+constexpr int kRoutePerThread = 32;                             // two 128-bit loads of mask bytes
+constexpr int kRouteTile = kRouteThreads * kRoutePerThread;     // 8192 tokens per tile
+constexpr int kLookPerLane = 4;                                 // look-back window: 32 lanes x 4 tiles
 
 // tile state word: [31:30] flag (0 = nothing, 1 = tile aggregate, 2 = inclusive prefix), [29:0] visual count
 constexpr uint32_t kFlagAgg = 1u << 30;
@@ -31,27 +32,29 @@ constexpr uint32_t kValMask = (1u << 30) - 1;
 
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __restrict__ mask, int M, int cap,
                                                               int* __restrict__ perm, int* __restrict__ counts,
-                                                              uint32_t* __restrict__ ws,  // [0] ticket, [1..] tile state
+                                                              uint32_t* __restrict__ ws,  // [0] unused, [1..] tile state
                                                               int* __restrict__ status) {
   __shared__ int s_list[kRouteTile];  // visual indices from the front, text indices after them
   __shared__ int s_warp[kRouteThreads / 32];
-  __shared__ int s_tile, s_excl, s_ok;
+  __shared__ int s_excl, s_ok;
 
   const int tid = threadIdx.x;
-  if (tid == 0) s_tile = static_cast<int>(atomicAdd(&ws[0], 1u));
-  __syncthreads();
-  const int tile = s_tile;
+  // Tiles are taken in block-index order.  Blocks are dispatched in that order, so a tile's
+  // predecessors are running or done when it looks back; the look-back wait is bounded regardless.
+  const int tile = blockIdx.x;
   const int num_tiles = (M + kRouteTile - 1) / kRouteTile;
   volatile uint32_t* state = ws + 1;
 
   const int base = tile * kRouteTile + tid * kRoutePerThread;
-  // 16 mask bytes of this thread
-  uint32_t w[4] = {0, 0, 0, 0};
+  // 32 mask bytes of this thread
+  uint32_t w[kRoutePerThread / 4] = {};
   int valid = M - base;
   valid = valid < 0 ? 0 : (valid > kRoutePerThread ? kRoutePerThread : valid);
   if (valid == kRoutePerThread && ((reinterpret_cast<uintptr_t>(mask) & 15) == 0)) {
-    const uint4 v = *reinterpret_cast<const uint4*>(mask + base);
-    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    const uint4 v0 = *reinterpret_cast<const uint4*>(mask + base);
+    const uint4 v1 = *reinterpret_cast<const uint4*>(mask + base + 16);
+    w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w;
+    w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
   } else {
     for (int i = 0; i < valid; ++i) w[i >> 2] |= static_cast<uint32_t>(mask[base + i]) << (8 * (i & 3));
   }
@@ -92,34 +95,48 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
     }
   }
   if (tile > 0 && tid < 32) {
-    // warp 0 walks back 32 tiles at a time
+    // warp 0 walks back 128 tiles at a time (lane l inspects tiles look - 4l - j, j = 0..3): the
+    // chain of inclusive prefixes then advances by up to 128 tiles per L2 round trip
     int excl = 0, ok = 1;
     int look = tile - 1;
     const uint64_t t0 = globaltimer_ns();
     while (true) {
-      const int idx = look - static_cast<int>(tid);
-      uint32_t s = 2u << 30;  // before tile 0: an inclusive prefix of 0
-      if (idx >= 0) s = state[idx];
+      uint32_t st[kLookPerLane];
+      int idx[kLookPerLane];
+#pragma unroll
+      for (int j = 0; j < kLookPerLane; ++j) {
+        idx[j] = look - (static_cast<int>(tid) * kLookPerLane + j);
+        st[j] = 2u << 30;  // before tile 0: an inclusive prefix of 0
+        if (idx[j] >= 0) st[j] = state[idx[j]];
+      }
       // wait until every inspected tile has published something (all branches warp-uniform)
       uint32_t polls = 0;
       while (true) {
-        const bool pending = idx >= 0 && (s >> 30) == 0;
+        bool pending = false;
+#pragma unroll
+        for (int j = 0; j < kLookPerLane; ++j) pending |= (st[j] >> 30) == 0;
         if (!__any_sync(0xFFFFFFFFu, pending)) break;
-        if (pending) s = state[idx];
+#pragma unroll
+        for (int j = 0; j < kLookPerLane; ++j)
+          if ((st[j] >> 30) == 0) st[j] = state[idx[j]];
         ++polls;
         const bool expired = (polls & 63u) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs;
         if (__any_sync(0xFFFFFFFFu, expired)) { ok = 0; break; }
       }
       if (!ok) break;
-      const uint32_t inc_ballot = __ballot_sync(0xFFFFFFFFu, (s >> 30) == 2);
-      // lanes nearer than the first inclusive prefix contribute their aggregate; that lane its prefix
-      const int first_inc = inc_ballot ? (__ffs(inc_ballot) - 1) : 32;
-      int contrib = (static_cast<int>(tid) <= first_inc) ? static_cast<int>(s & kValMask) : 0;
+      // nearest inclusive prefix in the window; nearer tiles contribute their aggregates, it its prefix
+      int my_first = 1 << 20;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xFFFFFFFFu, contrib, o);
-      excl += contrib;
-      if (inc_ballot) break;
-      look -= 32;
+      for (int j = kLookPerLane - 1; j >= 0; --j)
+        if ((st[j] >> 30) == 2) my_first = static_cast<int>(tid) * kLookPerLane + j;
+      const int first_inc = __reduce_min_sync(0xFFFFFFFFu, my_first);
+      int contrib = 0;
+#pragma unroll
+      for (int j = 0; j < kLookPerLane; ++j)
+        if (static_cast<int>(tid) * kLookPerLane + j <= first_inc) contrib += static_cast<int>(st[j] & kValMask);
+      excl += __reduce_add_sync(0xFFFFFFFFu, contrib);
+      if (first_inc < (1 << 20)) break;
+      look -= 32 * kLookPerLane;
     }
     if (tid == 0) {
       s_excl = excl;
@@ -260,12 +277,12 @@ extern "C" int ffnk_permute_rows(const void* x, int64_t ldx, const int32_t* perm
 // execute callback is given all its buffers up front and is forbidden to allocate device memory,
 // or a steady-state serving loop that must not touch cudaMalloc because it synchronises the
 // whole device.  For them the scan state lives in the fixed array below.  It is part of the
-// library image, so every GPU that loads the library carries these 16.25 KiB until the process
+// library image, so every GPU that loads the library carries these 8.25 KiB until the process
 // exits, and it bounds the mask length at FFNK_ROUTE_NOALLOC_MAX_TOKENS.
 // -------------------------------------------------------------------------------------------
 namespace ffnk {
 constexpr int64_t kNoAllocMaxTokens = FFNK_ROUTE_NOALLOC_MAX_TOKENS;
-constexpr int64_t kNoAllocWords = 1 + (kNoAllocMaxTokens + kRouteTile - 1) / kRouteTile;   // ticket + tile states
+constexpr int64_t kNoAllocWords = 1 + (kNoAllocMaxTokens + kRouteTile - 1) / kRouteTile;   // one spare word + tile states
 constexpr int64_t kNoAllocWordsPadded = ((kNoAllocWords + 63) / 64) * 64;
 
 static __device__ __align__(256) uint32_t g_route_scratch[kNoAllocWordsPadded];
@@ -309,7 +326,7 @@ extern "C" int ffnk_route_noalloc(const void* mask, int64_t M, int32_t* perm, in
   const int r = route_scratch_address(&scratch);
   if (r) return r;
   const int tiles = static_cast<int>((M + kRouteTile - 1) / kRouteTile);
-  // the array still holds the previous call's ticket and tile states: clear the part this call uses
+  // the array still holds the previous call's tile states: clear the part this call uses
   cudaError_t e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(tiles) + 1) * sizeof(uint32_t), stream);
   if (e != cudaSuccess) return cuda_status(e);
   route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,

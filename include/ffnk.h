@@ -68,7 +68,7 @@ int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* counts, void
  * or a steady-state loop that avoids cudaMalloc because it synchronises the device.
  *
  * Same results as ffnk_route() (perm, counts as described above) but without the workspace
- * argument: the scan state lives in a fixed 16.25 KiB array inside the library, which every GPU
+ * argument: the scan state lives in a fixed 8.25 KiB array inside the library, which every GPU
  * that loads the library keeps until the process exits.  Consequences:
  *   - M may not exceed FFNK_ROUTE_NOALLOC_MAX_TOKENS; a longer mask returns FFNK_ERR_CAPACITY
  *     and launches nothing.
