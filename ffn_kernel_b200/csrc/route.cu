@@ -199,8 +199,11 @@ extern "C" int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* c
   if (!mask || !perm || !workspace) return FFNK_ERR_NULL;
   if (reinterpret_cast<uintptr_t>(perm) & 15) return FFNK_ERR_ALIGN;
   const int tiles = static_cast<int>((M + kRouteTile - 1) / kRouteTile);
-  cudaError_t e = cudaMemsetAsync(workspace, 0, ffnk_route_workspace_bytes(M), stream);
-  if (e != cudaSuccess) return cuda_status(e);
+  // a single tile never looks back, so its state word need not be cleared
+  if (tiles > 1) {
+    cudaError_t e = cudaMemsetAsync(workspace, 0, ffnk_route_workspace_bytes(M), stream);
+    if (e != cudaSuccess) return cuda_status(e);
+  }
   route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,
                                                     counts, static_cast<uint32_t*>(workspace), status);
   return cuda_status(cudaGetLastError());
@@ -327,8 +330,10 @@ extern "C" int ffnk_route_noalloc(const void* mask, int64_t M, int32_t* perm, in
   if (r) return r;
   const int tiles = static_cast<int>((M + kRouteTile - 1) / kRouteTile);
   // the array still holds the previous call's tile states: clear the part this call uses
-  cudaError_t e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(tiles) + 1) * sizeof(uint32_t), stream);
-  if (e != cudaSuccess) return cuda_status(e);
+  if (tiles > 1) {
+    cudaError_t e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(tiles) + 1) * sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return cuda_status(e);
+  }
   route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,
                                                     counts, scratch, status);
   return cuda_status(cudaGetLastError());
