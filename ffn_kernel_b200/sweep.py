@@ -1,4 +1,4 @@
-"""Per-kernel timing sweep: the tool behind the tile table and the summaries in profiles/.
+"""Per-kernel timing sweep: the tool behind the tile table and the committed profile summaries.
 
     python -m ffn_kernel_b200.sweep ffn      --M 16384 --d 4096 --h 11008 [--mask span]
     python -m ffn_kernel_b200.sweep linear   --M 32768 --K 4096 --N 4096 [--mask span] [--bwd]

@@ -116,7 +116,9 @@ def ffn_case(TorchFFN, name, B, S, d, h, seed, with_grads=False):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
+    ref = sys.argv[1]
     TorchLinear, TorchFFN = _import_reference(ref)
     linear_case(TorchLinear, "linear_b2_s192_k64_n96", 2, 192, 64, 96, seed=1)
     linear_case(TorchLinear, "linear_b1_s200_k128_n192", 1, 200, 128, 192, seed=2)
