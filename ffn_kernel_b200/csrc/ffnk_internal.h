@@ -30,4 +30,9 @@ const DeviceInfo& device_info();
 int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride,
                        uint32_t box_inner, uint32_t box_outer);
 
+// permute_rows with an optional device-side gate: with only_if_scattered = T > 0 the kernel returns at
+// once unless the mask's runs of same-modality tokens average fewer than T rows.
+int permute_rows_launch(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out, int64_t ldo,
+                        int64_t M, int64_t d, int only_if_scattered, void* stream);
+
 }  // namespace ffnk

@@ -35,6 +35,15 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// Routing statistics (counts[3] = tokens, counts[4] = runs of consecutive same-modality tokens).
+// Gathering token rows inside a GEMM costs about 64 / (average run length) of its time (row tiles
+// that straddle a run boundary need many TMA instructions per k-step); copying the rows into routed
+// order first costs about 400 / (output columns).  The copy is taken when the average run is
+// shorter than `run_threshold` rows, which the host sets to max(32, columns / 6).
+__device__ __forceinline__ bool mask_is_scattered(const int* counts, int run_threshold) {
+  return static_cast<long long>(counts[4]) * run_threshold > counts[3];
+}
+
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
 // ---------------------------------------------------------------------------------------------

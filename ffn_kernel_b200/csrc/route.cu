@@ -6,7 +6,8 @@
 //
 //   perm[0 .. Mv)            = ascending indices of tokens with mask != 0   (visual)
 //   perm[cap .. cap + Mt)    = ascending indices of tokens with mask == 0   (text)
-//   counts[0] = Mv, counts[1] = Mt, counts[2] = cap, counts[3] = M
+//   counts[0] = Mv, counts[1] = Mt, counts[2] = cap, counts[3] = M,
+//   counts[4] = number of runs (maximal stretches of consecutive tokens of one modality); [5..7] unused
 //
 // Integer work, bit-exact with nonzero(mask) / nonzero(~mask).  One pass over the mask: a
 // chained scan with decoupled look-back over tiles in block-index order; the look-back spin is
@@ -32,11 +33,11 @@ constexpr uint32_t kValMask = (1u << 30) - 1;
 
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __restrict__ mask, int M, int cap,
                                                               int* __restrict__ perm, int* __restrict__ counts,
-                                                              uint32_t* __restrict__ ws,  // [0] unused, [1..] tile state
+                                                              uint32_t* __restrict__ ws,  // [0] run total, [1..tiles] tile state, [tiles+1] finished tiles
                                                               int* __restrict__ status) {
   __shared__ int s_list[kRouteTile];  // visual indices from the front, text indices after them
   __shared__ int s_warp[kRouteThreads / 32];
-  __shared__ int s_excl, s_ok;
+  __shared__ int s_excl, s_ok, s_runs;
 
   const int tid = threadIdx.x;
   // Tiles are taken in block-index order.  Blocks are dispatched in that order, so a tile's
@@ -63,6 +64,15 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
 #pragma unroll
   for (int i = 0; i < kRoutePerThread; ++i) bits |= (((w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0 ? 1u : 0u) << i;
   const int nv = __popc(bits);
+  // run starts among this thread's tokens: a token whose modality differs from its predecessor's
+  // (token 0 always).  The consumers use the total to tell span-structured masks from scattered ones.
+  int nruns = 0;
+  if (valid > 0) {
+    const uint32_t prev = base > 0 ? (mask[base - 1] != 0 ? 1u : 0u) : ((bits & 1u) ^ 1u);
+    const uint32_t vmask = valid == 32 ? 0xFFFFFFFFu : ((1u << valid) - 1u);
+    nruns = __popc((bits ^ ((bits << 1) | prev)) & vmask);
+  }
+  if (tid == 0) s_runs = 0;
 
   // block-wide exclusive scan of nv
   int incl = nv;
@@ -73,6 +83,10 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
   }
   if ((tid & 31) == 31) s_warp[tid >> 5] = incl;
   __syncthreads();
+  {
+    const int wr = __reduce_add_sync(0xFFFFFFFFu, nruns);
+    if ((tid & 31) == 0 && wr) atomicAdd(&s_runs, wr);
+  }
   int warp_off = 0, tile_v = 0;
 #pragma unroll
   for (int i = 0; i < kRouteThreads / 32; ++i) {
@@ -169,10 +183,21 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
     counts[2] = cap;
     counts[3] = M;
   }
+  if (tid == 0) {   // s_runs is complete: every warp added to it before the barrier above
+    if (num_tiles == 1) {
+      counts[4] = s_runs;
+    } else {
+      // the tile that finishes last publishes the total
+      atomicAdd(&ws[0], static_cast<uint32_t>(s_runs));
+      __threadfence();
+      if (atomicAdd(&ws[1 + num_tiles], 1u) == static_cast<uint32_t>(num_tiles - 1))
+        counts[4] = static_cast<int>(atomicAdd(&ws[0], 0u));
+    }
+  }
 }
 
 __global__ void route_empty_kernel(int* counts, int cap) {
-  counts[0] = 0; counts[1] = 0; counts[2] = cap; counts[3] = 0;
+  counts[0] = 0; counts[1] = 0; counts[2] = cap; counts[3] = 0; counts[4] = 0;
 }
 
 }  // namespace ffnk
@@ -183,7 +208,7 @@ extern "C" int64_t ffnk_route_capacity(int64_t M) { return ((M + 127) / 128) * 1
 
 extern "C" int64_t ffnk_route_workspace_bytes(int64_t M) {
   const int64_t tiles = (M + kRouteTile - 1) / kRouteTile;
-  return (tiles + 1) * static_cast<int64_t>(sizeof(uint32_t));
+  return (tiles + 2) * static_cast<int64_t>(sizeof(uint32_t));
 }
 
 extern "C" int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* counts, void* workspace,
@@ -227,7 +252,10 @@ __global__ void __launch_bounds__(kPermuteThreads) permute_rows_kernel(const uin
                                                                        const int* __restrict__ perm,
                                                                        const int* __restrict__ counts,
                                                                        uint4* __restrict__ out, int64_t ldo16,
-                                                                       int chunks) {
+                                                                       int chunks, int only_if_scattered) {
+  // optional gate (only_if_scattered = run-length threshold): the copy is wanted only when the mask
+  // is scattered; its consumer makes the same test with the same threshold
+  if (only_if_scattered && !mask_is_scattered(counts, only_if_scattered)) return;
   const int Mv = counts[0], Mt = counts[1], cap = counts[2];
   const int M = Mv + Mt;
   const int text_base = ((Mv + 255) >> 8) << 8;
@@ -255,8 +283,18 @@ __global__ void __launch_bounds__(kPermuteThreads) permute_rows_kernel(const uin
 }
 }  // namespace ffnk
 
+namespace ffnk {
+int permute_rows_launch(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out, int64_t ldo,
+                        int64_t M, int64_t d, int only_if_scattered, void* stream_);
+}
+
 extern "C" int ffnk_permute_rows(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out,
                                  int64_t ldo, int64_t M, int64_t d, void* stream_) {
+  return permute_rows_launch(x, ldx, perm, counts, out, ldo, M, d, 0, stream_);
+}
+
+int ffnk::permute_rows_launch(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out,
+                              int64_t ldo, int64_t M, int64_t d, int only_if_scattered, void* stream_) {
   if (M == 0) return 0;
   if (!x || !perm || !counts || !out) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || d < 8 || (d & 7) || d >= (1ll << 30)) return FFNK_ERR_SHAPE;
@@ -268,7 +306,7 @@ extern "C" int ffnk_permute_rows(const void* x, int64_t ldx, const int32_t* perm
   const int64_t max_blocks = static_cast<int64_t>(dev.sm_count) * 8;
   if (blocks > max_blocks) blocks = max_blocks;
   permute_rows_kernel<<<static_cast<unsigned>(blocks), kPermuteThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
-      static_cast<const uint4*>(x), ldx / 8, perm, counts, static_cast<uint4*>(out), ldo / 8, static_cast<int>(d / 8));
+      static_cast<const uint4*>(x), ldx / 8, perm, counts, static_cast<uint4*>(out), ldo / 8, static_cast<int>(d / 8), only_if_scattered);
   return cuda_status(cudaGetLastError());
 }
 
@@ -285,7 +323,7 @@ extern "C" int ffnk_permute_rows(const void* x, int64_t ldx, const int32_t* perm
 // -------------------------------------------------------------------------------------------
 namespace ffnk {
 constexpr int64_t kNoAllocMaxTokens = FFNK_ROUTE_NOALLOC_MAX_TOKENS;
-constexpr int64_t kNoAllocWords = 1 + (kNoAllocMaxTokens + kRouteTile - 1) / kRouteTile;   // one spare word + tile states
+constexpr int64_t kNoAllocWords = 2 + (kNoAllocMaxTokens + kRouteTile - 1) / kRouteTile;   // one spare word + tile states
 constexpr int64_t kNoAllocWordsPadded = ((kNoAllocWords + 63) / 64) * 64;
 
 static __device__ __align__(256) uint32_t g_route_scratch[kNoAllocWordsPadded];
@@ -331,7 +369,7 @@ extern "C" int ffnk_route_noalloc(const void* mask, int64_t M, int32_t* perm, in
   const int tiles = static_cast<int>((M + kRouteTile - 1) / kRouteTile);
   // the array still holds the previous call's tile states: clear the part this call uses
   if (tiles > 1) {
-    cudaError_t e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(tiles) + 1) * sizeof(uint32_t), stream);
+    cudaError_t e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(tiles) + 2) * sizeof(uint32_t), stream);
     if (e != cudaSuccess) return cuda_status(e);
   }
   route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,

@@ -81,6 +81,10 @@ struct GemmParams {
   __nv_bfloat16* aux0 = nullptr;
   __nv_bfloat16* aux1 = nullptr;
   __nv_bfloat16* aux2 = nullptr;
+  // Gather mode: when > 0, a routed-order copy of A exists (tensor map m[COPY_MAP]; permute_rows
+  // fills it only for scattered masks) and the kernel reads it instead of gathering whenever the
+  // mask's average run is shorter than a_copy rows -- decided on the device from counts[4].
+  int a_copy = 0;
   // Optional second contraction segment (A_ROUTED + EPI_STORE only): after k_len columns of the
   // first A matrix against the first weight, k_len1 columns of a second A matrix (tensor map
   // m[RUN_LEVELS - 1]) against the second weight (the "1" weight maps) go into the same accumulator.
@@ -89,10 +93,13 @@ struct GemmParams {
 
 // Views of one row-gathered activation matrix: m[0] fetches single rows (gather4); m[1 + i]
 // fetches boxes of 4 << i consecutive rows (4, 8, ..., 128), 64 columns wide.
+// m[RUN_LEVELS + 1] (gather mode only, optional) views a copy of the same matrix in routed order.
 constexpr int RUN_LEVELS = 6;
+constexpr int COPY_MAP = RUN_LEVELS + 1;
 struct AMaps {
-  CUtensorMap m[1 + RUN_LEVELS];
+  CUtensorMap m[2 + RUN_LEVELS];
 };
+
 
 // Run detection shared by the gathering producers.  Every lane holds four consecutive list
 // rows (r0..r3; `valid` = how many of them exist).  A block of 4n rows led by lane L (L a
@@ -304,7 +311,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
     }
     *abort_flag = 0;
     fence_mbar_init();
-    for (int i = 0; i <= RUN_LEVELS; ++i) tma_prefetch_desc(&am.m[i]);
+    for (int i = 0; i <= COPY_MAP; ++i) tma_prefetch_desc(&am.m[i]);
     tma_prefetch_desc(&tmBv0);
     tma_prefetch_desc(&tmBv1);
     tma_prefetch_desc(&tmBt0);
@@ -334,6 +341,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
     uint32_t phase = 0;
     int issued = 0;
     bool ok = true;
+    const bool via_copy = (A_MODE == A_GATHER) && p.a_copy && mask_is_scattered(p.counts, p.a_copy);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord tc = decode_tile(t, tiles_v, m_tiles, n_tiles, p.group_m, Mv, Mt, cap);
       int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
@@ -372,8 +380,14 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
         const bool seg1 = ks >= k_steps0;
         const int kx = (seg1 ? ks - k_steps0 : ks) * BK;
         if constexpr (A_MODE == A_GATHER) {
-          if (run_lanes == 0) tma_gather4(sa + lane * 512, &am.m[0], &full[stage], kx, r0, r1, r2, r3);
-          else if (run_lead) tma_load_2d(sa + lane * 512, run_map, &full[stage], kx, r0);
+          if (via_copy) {
+            if (lane == 0)
+              tma_load_2d(sa, &am.m[COPY_MAP], &full[stage], kx, (tc.text ? text_row_base(Mv) : 0) + tc.row0);
+          } else if (run_lanes == 0) {
+            tma_gather4(sa + lane * 512, &am.m[0], &full[stage], kx, r0, r1, r2, r3);
+          } else if (run_lead) {
+            tma_load_2d(sa + lane * 512, run_map, &full[stage], kx, r0);
+          }
         } else {
           if (lane == 0)
             tma_load_2d(sa, &am.m[seg1 ? RUN_LEVELS - 1 : RUN_LEVELS], &full[stage], kx,
@@ -547,7 +561,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
     }
     *abort_flag = 0;
     fence_mbar_init();
-    for (int i = 0; i <= RUN_LEVELS; ++i) tma_prefetch_desc(&am.m[i]);
+    for (int i = 0; i <= COPY_MAP; ++i) tma_prefetch_desc(&am.m[i]);
     tma_prefetch_desc(&tmBv0);
     tma_prefetch_desc(&tmBv1);
     tma_prefetch_desc(&tmBt0);
@@ -598,6 +612,7 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
     uint32_t phase = 0;
     bool ok = true;
     long long t_begin = clock64(), t_wait = 0;
+    const bool via_copy = (A_MODE == A_GATHER) && p.a_copy && mask_is_scattered(p.counts, p.a_copy);
     for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
       const TileCoord tc = cta_tile(t);
       int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
@@ -641,7 +656,9 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
         // otherwise both halves come from the segment's weight
         const CUtensorMap* mB = epi_glu(EPI) ? (rank ? mB1 : mB0) : (seg1 ? mB1 : mB0);
         if constexpr (A_MODE == A_GATHER) {
-          if (empty_half) {
+          if (via_copy) {
+            if (lane == 0) tma_load_2d_pair(sa, &am.m[COPY_MAP], lead_full, kx, (tc.text ? text_base : 0) + tc.row0);
+          } else if (empty_half) {
             if (lane == 0) tma_load_2d_pair(sa, &am.m[RUN_LEVELS], lead_full, kx, p.pad_row);
           } else if (run_lanes == 0) {
             tma_gather4_pair(sa + lane * 512, &am.m[0], lead_full, kx, r0, r1, r2, r3);
@@ -793,6 +810,16 @@ struct WgradParams {
   int max_run_rows;
   int* status;
   int routed = 0;   // 1: P and Q are in routed order (row = group base + list position), no index list
+  int copies = 0;   // > 0: routed-order copies of P and Q exist (second pair of maps) and are read instead
+                    //    whenever the mask's average run is shorter than this (decided on the device);
+                    //    their height is copy_rows
+  int copy_rows = 0;
+};
+
+// Views of one operand of the weight-gradient GEMM: m[0] single rows (gather4), m[1 + i] boxes of
+// 4 << i rows (4...64), 64 columns wide.
+struct WMaps {
+  CUtensorMap m[RUN_LEVELS];
 };
 
 struct WgradTile {
@@ -816,7 +843,8 @@ __device__ __forceinline__ WgradTile decode_wgrad_tile(int t, int p_tiles, int q
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS_MAX, 1)
-wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm, const WgradParams p) {
+wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm, const __grid_constant__ WMaps pmc,
+             const __grid_constant__ WMaps qmc, const WgradParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -843,6 +871,8 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
     for (int i = 0; i < RUN_LEVELS; ++i) {
       tma_prefetch_desc(&pm.m[i]);
       tma_prefetch_desc(&qm.m[i]);
+      tma_prefetch_desc(&pmc.m[i]);
+      tma_prefetch_desc(&qmc.m[i]);
     }
   }
   if (warp == 1) {
@@ -865,6 +895,11 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
     uint32_t phase = 0;
     int issued = 0;
     bool ok = true;
+    const bool use_copies = p.copies && mask_is_scattered(p.counts, p.copies);
+    const bool routed = p.routed || use_copies;
+    const WMaps* mp = use_copies ? &pmc : &pm;
+    const WMaps* mq = use_copies ? &qmc : &qm;
+    const int pad_row = use_copies ? p.copy_rows : p.pad_row;
     const int gi = lane & 15;     // which group of four list rows inside the k-step
     const int half = lane >> 4;   // which 64-column block (of a pair)
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -872,19 +907,19 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
       if (wt.cnt == 0) continue;
       const int k_steps = (wt.cnt + BK - 1) / BK;
       const int* list = p.perm + wt.list_off;
-      const int4 pad4 = make_int4(p.pad_row, p.pad_row, p.pad_row, p.pad_row);
+      const int4 pad4 = make_int4(pad_row, pad_row, pad_row, pad_row);
       const int group_base = wt.text ? text_row_base(Mv) : 0;
-      int4 nxt = (!p.routed && 4 * gi < wt.cnt) ? *reinterpret_cast<const int4*>(list + 4 * gi) : pad4;
+      int4 nxt = (!routed && 4 * gi < wt.cnt) ? *reinterpret_cast<const int4*>(list + 4 * gi) : pad4;
       for (int ks = 0; ks < k_steps; ++ks) {
         const int lr = ks * BK + 4 * gi;
         int4 v = nxt;
-        if (p.routed) {
+        if (routed) {
           v = make_int4(group_base + lr, group_base + lr + 1, group_base + lr + 2, group_base + lr + 3);
         } else if (ks + 1 < k_steps) {
           // the next k-step's rows are requested now so that the load is hidden behind this step
           nxt = (lr + BK < wt.cnt) ? *reinterpret_cast<const int4*>(list + lr + BK) : pad4;
         }
-        int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
+        int r0 = pad_row, r1 = pad_row, r2 = pad_row, r3 = pad_row;
         const int valid = min(4, max(0, wt.cnt - lr));
         if (valid > 0) {
           r0 = v.x;
@@ -914,13 +949,13 @@ wgrad_kernel(const __grid_constant__ AMaps pm, const __grid_constant__ AMaps qm,
         uint8_t* dq1 = sq + (2 + half) * 8192 + gi * 512;
         const int cp = wt.pt * BM + half * 64, cq0 = wt.qt * BN + half * 64, cq1 = wt.qt * BN + (2 + half) * 64;
         if (run_lanes == 0) {
-          tma_gather4(dp, &pm.m[0], &full[stage], cp, r0, r1, r2, r3);
-          tma_gather4(dq0, &qm.m[0], &full[stage], cq0, r0, r1, r2, r3);
-          tma_gather4(dq1, &qm.m[0], &full[stage], cq1, r0, r1, r2, r3);
+          tma_gather4(dp, &mp->m[0], &full[stage], cp, r0, r1, r2, r3);
+          tma_gather4(dq0, &mq->m[0], &full[stage], cq0, r0, r1, r2, r3);
+          tma_gather4(dq1, &mq->m[0], &full[stage], cq1, r0, r1, r2, r3);
         } else if (run_lead) {
-          tma_load_2d(dp, &pm.m[level], &full[stage], cp, r0);
-          tma_load_2d(dq0, &qm.m[level], &full[stage], cq0, r0);
-          tma_load_2d(dq1, &qm.m[level], &full[stage], cq1, r0);
+          tma_load_2d(dp, &mp->m[level], &full[stage], cp, r0);
+          tma_load_2d(dq0, &mq->m[level], &full[stage], cq0, r0);
+          tma_load_2d(dq1, &mq->m[level], &full[stage], cq1, r0);
         }
         ++issued;
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -1070,6 +1105,7 @@ static int weight_map(CUtensorMap* m, const WeightView& w, bool* mn_major, int b
 static int gather_maps(AMaps& a, const void* base, int64_t cols, int64_t rows, int64_t ld) {
   int r = make_tensor_map_2d(&a.m[0], base, cols, rows, ld, BK, 1);
   for (int i = 0; i < RUN_LEVELS && !r; ++i) r = make_tensor_map_2d(&a.m[1 + i], base, cols, rows, ld, BK, 4u << i);
+  a.m[COPY_MAP] = a.m[RUN_LEVELS];
   return r;
 }
 
@@ -1192,22 +1228,45 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
 // out_g[p, q] = sum over the rows of modality g of P[row, p] * Q[row, q], for both modalities.
 // rows: token rows picked through the routing lists, or (routed != 0) rows of matrices that are
 // already in routed order.  `rows_total` is the height of P and Q.
+// Average run length below which a routed-order copy beats gathering rows inside a GEMM with
+// `columns` output columns (see mask_is_scattered).
+static int copy_threshold(int64_t columns) {
+  const int64_t t = columns / 6;
+  return static_cast<int>(t < 32 ? 32 : (t > 4096 ? 4096 : t));
+}
+
+static int wgrad_maps(WMaps& w, const void* base, int64_t cols, int64_t rows, int64_t ld) {
+  int r = make_tensor_map_2d(&w.m[0], base, cols, rows, ld, BK, 1);
+  for (int i = 1; i < RUN_LEVELS && !r; ++i) r = make_tensor_map_2d(&w.m[i], base, cols, rows, ld, BK, 2u << i);
+  return r;
+}
+
 static int launch_wgrad(const void* P, int64_t ldp, int64_t p_dim, const void* Q, int64_t ldq, int64_t q_dim,
                         int64_t rows_total, void* out_v, void* out_t, int64_t ldo, int routed, const int32_t* perm,
-                        const int32_t* counts, int32_t* status, cudaStream_t s) {
+                        const int32_t* counts, int32_t* status, cudaStream_t s, const void* P_copy = nullptr,
+                        const void* Q_copy = nullptr, int64_t copy_rows = 0, int copy_thr = 0) {
   const DeviceInfo& dev = device_info();
-  AMaps tmP, tmQ;
-  int r = gather_maps(tmP, P, p_dim, rows_total, ldp);
+  WMaps tmP, tmQ, tmPc, tmQc;
+  int r = wgrad_maps(tmP, P, p_dim, rows_total, ldp);
   if (r) return r;
-  if ((r = gather_maps(tmQ, Q, q_dim, rows_total, ldq))) return r;
+  if ((r = wgrad_maps(tmQ, Q, q_dim, rows_total, ldq))) return r;
+  const bool copies = P_copy && Q_copy;
+  if (copies) {
+    if ((r = wgrad_maps(tmPc, P_copy, p_dim, copy_rows, p_dim))) return r;
+    if ((r = wgrad_maps(tmQc, Q_copy, q_dim, copy_rows, q_dim))) return r;
+  } else {
+    tmPc = tmP;
+    tmQc = tmQ;
+  }
   WgradParams wp{perm, counts, static_cast<__nv_bfloat16*>(out_v), static_cast<__nv_bfloat16*>(out_t), ldo,
                  static_cast<int>(p_dim), static_cast<int>(q_dim), static_cast<int>(rows_total),
-                 max_run_rows() < 64 ? max_run_rows() : 64, status, routed};
+                 max_run_rows() < 64 ? max_run_rows() : 64, status, routed, copies ? copy_thr : 0,
+                 static_cast<int>(copy_rows)};
   int64_t grid = 2 * ((p_dim + BM - 1) / BM) * ((q_dim + BN - 1) / BN);
   if (grid > usable_sms(dev)) grid = usable_sms(dev);
   cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
   if (e != cudaSuccess) return cuda_status(e);
-  wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
+  wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, tmPc, tmQc, wp);
   return cuda_status(cudaGetLastError());
 }
 
@@ -1219,7 +1278,7 @@ using namespace ffnk;
 
 extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const void* b2, int64_t b_stride_k,
                                int64_t b_stride_n, const int32_t* perm, const int32_t* counts, void* c, int64_t ldc,
-                               int64_t M, int64_t N, int64_t K, int32_t* status, void* stream) {
+                               void* a_copy, int64_t M, int64_t N, int64_t K, int32_t* status, void* stream) {
   if (M == 0) return 0;
   if (!a || !b1 || !b2 || !perm || !counts || !c) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(N) || bad_dim(K)) return FFNK_ERR_SHAPE;
@@ -1228,6 +1287,12 @@ extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const
   CUtensorMap tmB[4];
   int r = gather_maps(tmA, a, K, M, lda);
   if (r) return r;
+  if (a_copy) {
+    // scattered masks: a routed-order copy of A (made only then) replaces the row gather
+    if (reinterpret_cast<uintptr_t>(a_copy) & 15) return FFNK_ERR_ALIGN;
+    if ((r = permute_rows_launch(a, lda, perm, counts, a_copy, K, M, K, copy_threshold(N), stream))) return r;
+    if ((r = make_tensor_map_2d(&tmA.m[COPY_MAP], a_copy, K, ffnk_route_capacity(M) + 512, K, BK, BM))) return r;
+  }
   bool mn1 = false, mn2 = false;
   const TileChoice tile = pick_tile(M, N, A_GATHER, EPI_STORE, weights_k_major(b_stride_k, b_stride_n, K));
   if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_k, b_stride_n, K, N}, &mn1, tile.bn / 2))) return r;
@@ -1236,6 +1301,7 @@ extern "C" int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(c), ldc, static_cast<int>(N), static_cast<int>(K),
                static_cast<int>(M), pick_group_m(K), max_run_rows(), status, g_prof_buffer};
+  p.a_copy = a_copy ? copy_threshold(N) : 0;
   return launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, static_cast<cudaStream_t>(stream));
 }
 
@@ -1253,7 +1319,8 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
   if (routed_in) {
     // x is [(cap + 512), d] in routed order (ffnk_permute_rows): one tiled box per A tile
     r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], x, d, ffnk_route_capacity(M) + 512, ldx, BK, BM);
-    for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+    for (int i = 0; i <= COPY_MAP; ++i)
+      if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
   } else {
     r = gather_maps(tmA, x, d, M, ldx);
   }
@@ -1288,7 +1355,8 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   CUtensorMap tmB[4];
   int r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], inter, h, rows, ldi, BK, BM);
   if (r) return r;
-  for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+  for (int i = 0; i <= COPY_MAP; ++i)
+      if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
   bool mn1 = false, mn2 = false;
   const TileChoice tile = pick_tile(M, d, A_ROUTED, EPI_STORE, weights_k_major(w_stride_k, w_stride_n, h));
   if ((r = weight_map(&tmB[0], WeightView{w2, w_stride_k, w_stride_n, h, d}, &mn1, tile.bn / 2))) return r;
@@ -1302,8 +1370,8 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
 
 extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
                                int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm, const int32_t* counts,
-                               void* da, int64_t ldda, void* db1, void* db2, int64_t M, int64_t N, int64_t K,
-                               int32_t* status, void* stream) {
+                               void* da, int64_t ldda, void* db1, void* db2, void* g_copy, void* a_copy, int64_t M,
+                               int64_t N, int64_t K, int32_t* status, void* stream) {
   if (!db1 || !db2) return FFNK_ERR_NULL;
   if (bad_dim(N) || bad_dim(K) || M < 0 || M >= (1ll << 30)) return FFNK_ERR_SHAPE;
   const bool k_major = (b_stride_k == 1 && b_stride_n >= K);   // storage [N, K]
@@ -1325,12 +1393,22 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
   const DeviceInfo& dev = device_info();
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
 
+  // scattered masks: routed-order copies of g and a (made only then) replace every row gather below
+  const bool copies = g_copy && a_copy;
+  const int64_t copy_rows = ffnk_route_capacity(M) + 512;
+  const int thr = copy_threshold((N + K) / 2);   // one decision shared by the dx GEMM and the weight gradients
+  if (copies && ((reinterpret_cast<uintptr_t>(g_copy) | reinterpret_cast<uintptr_t>(a_copy)) & 15)) return FFNK_ERR_ALIGN;
   // dx: the forward kernel on g with the weights seen as [N, K] (contraction over N)
   {
     AMaps tmA;
     CUtensorMap tmB[4];
     int r = gather_maps(tmA, g, N, M, ldg);
     if (r) return r;
+    if (copies) {
+      if ((r = permute_rows_launch(g, ldg, perm, counts, g_copy, N, M, N, thr, stream))) return r;
+      if ((r = permute_rows_launch(a, lda, perm, counts, a_copy, K, M, K, thr, stream))) return r;
+      if ((r = make_tensor_map_2d(&tmA.m[COPY_MAP], g_copy, N, copy_rows, N, BK, BM))) return r;
+    }
     bool mn1 = false, mn2 = false;
     const TileChoice tile = pick_tile(M, K, A_GATHER, EPI_STORE, weights_k_major(b_stride_n, b_stride_k, N));
     if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_n, b_stride_k, N, K}, &mn1, tile.bn / 2))) return r;
@@ -1339,6 +1417,7 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     tmB[3] = tmB[2];
     GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(da), ldda, static_cast<int>(K), static_cast<int>(N),
                  static_cast<int>(M), pick_group_m(N), max_run_rows(), status, g_prof_buffer};
+    p.a_copy = copies ? thr : 0;
     r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, s);
     if (r) return r;
   }
@@ -1349,7 +1428,8 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     const int64_t ldp = k_major ? ldg : lda, ldq = k_major ? lda : ldg;
     const int64_t p_dim = k_major ? N : K, q_dim = k_major ? K : N;
     return launch_wgrad(P, ldp, p_dim, Q, ldq, q_dim, M, db1, db2, k_major ? b_stride_n : b_stride_k, 0, perm, counts,
-                        status, s);
+                        status, s, copies ? (k_major ? g_copy : a_copy) : nullptr,
+                        copies ? (k_major ? a_copy : g_copy) : nullptr, copy_rows, thr);
   }
 }
 
@@ -1389,7 +1469,8 @@ extern "C" int ffnk_ffn_forward_train(const void* x, int64_t ldx, const void* w1
     AMaps tmA;
     CUtensorMap tmB[4];
     if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], xr, d, rows, d, BK, BM))) return r;
-    for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+    for (int i = 0; i <= COPY_MAP; ++i)
+      if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
     bool mn = false, mn_i = false;
     const void* ws[4] = {w1, w3, u1, u3};
     const TileChoice tile = pick_tile(M, h, A_ROUTED, EPI_SWIGLU_SAVE, weights_k_major(w13_stride_k, w13_stride_n, d));
@@ -1434,7 +1515,8 @@ extern "C" int ffnk_ffn_backward(const void* gy, int64_t ldg, const void* xr, co
     AMaps tmA;
     CUtensorMap tmB[4];
     if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], gr, d, rows, d, BK, BM))) return r;
-    for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+    for (int i = 0; i <= COPY_MAP; ++i)
+      if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
     bool mn1 = false, mn2 = false;
     const TileChoice tile = pick_tile(M, h, A_ROUTED, EPI_DSWIGLU, weights_k_major(w2_stride_n, w2_stride_k, d));
     if ((r = weight_map(&tmB[0], WeightView{w2, w2_stride_n, w2_stride_k, d, h}, &mn1, tile.bn / 2))) return r;
@@ -1464,7 +1546,8 @@ extern "C" int ffnk_ffn_backward(const void* gy, int64_t ldg, const void* xr, co
     AMaps tmA;
     CUtensorMap tmB[4];
     if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], dt1, h, rows, h, BK, BM))) return r;
-    for (int i = 0; i < RUN_LEVELS; ++i) tmA.m[i] = tmA.m[RUN_LEVELS];
+    for (int i = 0; i <= COPY_MAP; ++i)
+      if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
     if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS - 1], dt3, h, rows, h, BK, BM))) return r;
     bool mn = false, mn_i = false;
     const void* ws[4] = {w1, w3, u1, u3};

@@ -154,7 +154,7 @@ def _bf16_ffn_train_forward(x, w1, w2, w3, u1, u2, u3, mask):
         cap = int(L.ffnk_route_capacity(M))
         rows = cap + 512
         perm = torch.empty(max(2 * cap, 4), dtype=torch.int32, device=dev)
-        counts = torch.empty(4, dtype=torch.int32, device=dev)
+        counts = torch.empty(8, dtype=torch.int32, device=dev)
         xr = torch.empty((rows, d), device=dev, dtype=torch.bfloat16)
         t1, t3, hid = (torch.empty((rows, h), device=dev, dtype=torch.bfloat16) for _ in range(3))
         saved = dict(M=M, d=d, h=h, perm=perm, counts=counts, xr=xr, t1=t1, t3=t3, hid=hid,

@@ -8,6 +8,8 @@ CUDA).  Tile shapes are fixed per kernel in the library, not looked up from a co
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ._lib import check, lib
@@ -73,6 +75,23 @@ def _mask_route(mask, M, device, rt: Route | None) -> Route:
     return route(mask)
 
 
+def _copy_scratch(M: int, width: int, dev):
+    """Scratch for a routed-order copy of an [M, width] activation, or None for small M.
+
+    The library fills and reads it only when the routing statistics say the mask is scattered
+    (runs of same-modality tokens averaging under max(32, columns / 6) rows); masks made of long
+    spans never touch it.
+    FFNK_LINEAR_COPY=0 withholds it (the GEMM then always gathers token rows itself)."""
+    if os.environ.get("FFNK_LINEAR_COPY", "1") == "0" or M < 512:
+        return None
+    cap = int(lib().ffnk_route_capacity(M))
+    return torch.empty((cap + 512, width), device=dev, dtype=torch.bfloat16)
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
 def _bf16_linear_forward(a, b1, b2, mask, rt: Route | None = None):
     """c[m] = a[m] @ (b1 if mask[m] else b2).  a [M,K], b1/b2 [K,N], mask [M] -> [M,N] bf16."""
     a = _activation(a, "a")
@@ -86,9 +105,10 @@ def _bf16_linear_forward(a, b1, b2, mask, rt: Route | None = None):
         if M == 0:
             return c
         rt = _mask_route(mask, M, dev, rt)
+        a_copy = _copy_scratch(M, K, dev)
         check("ffnk_linear_fwd", lib().ffnk_linear_fwd(
             a.data_ptr(), a.stride(0), b1.data_ptr(), b2.data_ptr(), b1.stride(0), b1.stride(1),
-            rt.perm.data_ptr(), rt.counts.data_ptr(), c.data_ptr(), c.stride(0), M, N, K,
+            rt.perm.data_ptr(), rt.counts.data_ptr(), c.data_ptr(), c.stride(0), _ptr(a_copy), M, N, K,
             status_word(dev).data_ptr(), stream_ptr(dev)))
     maybe_check(dev)
     return c
@@ -116,10 +136,11 @@ def _bf16_linear_backward(gd, a, b1, b2, mask, rt: Route | None = None):
         if M == 0:
             return da, db1.zero_(), db2.zero_()
         rt = _mask_route(mask, M, dev, rt)
+        g_copy, a_copy = _copy_scratch(M, N, dev), _copy_scratch(M, K, dev)
         check("ffnk_linear_bwd", lib().ffnk_linear_bwd(
             gd.data_ptr(), gd.stride(0), a.data_ptr(), a.stride(0), b1.data_ptr(), b2.data_ptr(),
             b1.stride(0), b1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(),
-            da.data_ptr(), da.stride(0), db1.data_ptr(), db2.data_ptr(), M, N, K,
+            da.data_ptr(), da.stride(0), db1.data_ptr(), db2.data_ptr(), _ptr(g_copy), _ptr(a_copy), M, N, K,
             status_word(dev).data_ptr(), stream_ptr(dev)))
     maybe_check(dev)
     return da, db1, db2

@@ -57,7 +57,7 @@ def maybe_check(device) -> None:
 class Route:
     """Device-resident routing lists for one mask (see ``include/ffnk.h``, ffnk_route)."""
     perm: torch.Tensor     # int32 [2 * cap]
-    counts: torch.Tensor   # int32 [4] = Mv, Mt, cap, M
+    counts: torch.Tensor   # int32 [8] = Mv, Mt, cap, M, runs, (unused)
     M: int
     cap: int
 
@@ -81,7 +81,7 @@ def route(mask: torch.Tensor) -> Route:
     cap = int(L.ffnk_route_capacity(M))
     with torch.cuda.device(dev):
         perm = torch.empty(max(2 * cap, 4), dtype=torch.int32, device=dev)
-        counts = torch.empty(4, dtype=torch.int32, device=dev)
+        counts = torch.empty(8, dtype=torch.int32, device=dev)
         ws = torch.empty(max(int(L.ffnk_route_workspace_bytes(M)), 4), dtype=torch.uint8, device=dev)
         check("ffnk_route", L.ffnk_route(mask.data_ptr(), M, perm.data_ptr(), counts.data_ptr(), ws.data_ptr(),
                                          status_word(dev).data_ptr(), stream_ptr(dev)))

@@ -49,15 +49,15 @@ def test_pure_host_functions(libffnk):
 def test_argument_errors_are_reported_before_any_launch(libffnk):
     L = libffnk
     # null pointers
-    assert L.ffnk_linear_fwd(None, 8, None, None, 1, 8, None, None, None, 8, 16, 8, 8, None, None) == -1
+    assert L.ffnk_linear_fwd(None, 8, None, None, 1, 8, None, None, None, 8, None, 16, 8, 8, None, None) == -1
     assert L.ffnk_ffn_down(None, 8, None, None, 1, 8, None, None, None, 8, 16, 8, 8, None, None) == -1
     assert L.ffnk_route(None, 16, None, None, None, None, None) == -1
     # sizes: not a multiple of 8 / negative
     fake = ctypes.c_void_p(0x1000)
-    assert L.ffnk_linear_fwd(fake, 8, fake, fake, 1, 8, fake, fake, fake, 8, 16, 12, 8, fake, None) == -2
-    assert L.ffnk_linear_fwd(fake, 8, fake, fake, 1, 8, fake, fake, fake, 8, -1, 8, 8, fake, None) == -2
+    assert L.ffnk_linear_fwd(fake, 8, fake, fake, 1, 8, fake, fake, fake, 8, None, 16, 12, 8, fake, None) == -2
+    assert L.ffnk_linear_fwd(fake, 8, fake, fake, 1, 8, fake, fake, fake, 8, None, -1, 8, 8, fake, None) == -2
     # misaligned leading dimension
-    assert L.ffnk_linear_fwd(fake, 9, fake, fake, 1, 8, fake, fake, fake, 8, 16, 8, 8, fake, None) == -3
+    assert L.ffnk_linear_fwd(fake, 9, fake, fake, 1, 8, fake, fake, fake, 8, None, 16, 8, 8, fake, None) == -3
     # decode: too many tokens, wrong weight layout
     n = L.ffnk_decode_max_tokens()
     args = [fake, 8, fake, fake, fake, fake, fake, fake, 1, 8, 1, 8, fake, fake, fake, 8]
@@ -65,7 +65,7 @@ def test_argument_errors_are_reported_before_any_launch(libffnk):
     args[8], args[9] = 8, 1
     assert L.ffnk_ffn_decode(*args, 1, 8, 8, fake, None) == -4
     # empty problems succeed without touching the device
-    assert L.ffnk_linear_fwd(None, 8, None, None, 1, 8, None, None, None, 8, 0, 8, 8, None, None) == 0
+    assert L.ffnk_linear_fwd(None, 8, None, None, 1, 8, None, None, None, 8, None, 0, 8, 8, None, None) == 0
 
 
 def test_python_wrappers_refuse_cpu_tensors():

@@ -152,3 +152,26 @@ def test_full_size_rows_sampled(dev):
     ref = O.masked_linear(c.x[rows], c.wv.T, c.wt.T, c.mask[rows])
     assert O.max_rel_err(y[rows.to(dev)], ref) < TOL
     assert bool(torch.isfinite(y.float()).all())
+
+
+@pytest.mark.parametrize("kind", ["bernoulli", "alternating", "span"])
+def test_scattered_masks_with_and_without_the_routed_copy(dev, kind, monkeypatch):
+    # with the scratch the library copies rows into routed order for scattered masks only; without
+    # it the GEMMs gather every row themselves: both must give the same gradients and outputs
+    from ffn_kernel_b200.linear import _bf16_linear_backward, _bf16_linear_forward
+    M, K, N = 2000, 264, 328
+    c = linear_case(M, K, N, seed=11, mask=edge_mask(M, kind, seed=5), with_grad=True)
+    ref_y = O.masked_linear(c.x, c.wv.T, c.wt.T, c.mask)
+    ref_g = O.masked_linear_backward(c.g, c.x, c.wv.T, c.wt.T, c.mask)
+    g = c.to(dev)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("FFNK_LINEAR_COPY", flag)
+        y = _bf16_linear_forward(g.x, g.wv.T, g.wt.T, g.mask)
+        grads = _bf16_linear_backward(g.g, g.x, g.wv.T, g.wt.T, g.mask)
+        check_status()
+        assert O.max_rel_err(y, ref_y) < TOL
+        for got, ref in zip(grads, ref_g):
+            assert O.max_rel_err(got, ref) < TOL
+        outs.append((y, *grads))
+    assert torch.equal(outs[0][0], outs[1][0])        # forward rows are the same sums either way

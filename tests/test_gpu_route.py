@@ -18,7 +18,9 @@ def _check(mask_cpu, dev):
     assert v.dtype == torch.int32 and t.dtype == torch.int32
     assert np.array_equal(v.cpu().numpy(), ov)
     assert np.array_equal(t.cpu().numpy(), ot)
-    assert rt.counts.tolist() == [len(ov), len(ot), rt.cap, mask_cpu.numel()]
+    m = np.asarray(mask_cpu.numpy() != 0)
+    runs = int(m.size > 0) + int(np.count_nonzero(m[1:] != m[:-1]))
+    assert rt.counts.tolist()[:5] == [len(ov), len(ot), rt.cap, mask_cpu.numel(), runs]
 
 
 @pytest.mark.parametrize("M", [1, 2, 15, 16, 17, 127, 128, 129, 1000, 4095, 4096, 4097, 4099, 8192, 65537, 1 << 20])
