@@ -34,6 +34,10 @@ SIGNATURES = {
                                 c_void_p, c_void_p]),
     "ffnk_ffn_down": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
                               c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ffnk_ffn_down_to_peers": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p,
+                                       POINTER(c_void_p), c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                       c_void_p, c_void_p]),
+    "ffnk_sum_row_blocks": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
     "ffnk_decode_max_tokens": (c_int, []),
     "ffnk_ffn_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,

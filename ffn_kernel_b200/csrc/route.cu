@@ -14,6 +14,8 @@
 // bounded, so a tile whose predecessor never publishes reports a status code instead of hanging.
 //
 // Algorithmic traffic: 1 byte read + 4 bytes written per token.
+#include <cuda_bf16.h>
+
 #include <mutex>
 
 #include "ffnk_internal.h"
@@ -308,6 +310,64 @@ int ffnk::permute_rows_launch(const void* x, int64_t ldx, const int32_t* perm, c
   permute_rows_kernel<<<static_cast<unsigned>(blocks), kPermuteThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
       static_cast<const uint4*>(x), ldx / 8, perm, counts, static_cast<uint4*>(out), ldo / 8, static_cast<int>(d / 8), only_if_scattered);
   return cuda_status(cudaGetLastError());
+}
+
+// -------------------------------------------------------------------------------------------
+// Sum of row blocks: out[r, c] = sum over b of blocks[b][r][c], bf16 in, fp32 sum, bf16 out.
+// Second half of the tensor-parallel reduce-scatter whose first half is the down projection that
+// writes every rank's partial rows into their owner's memory (ffnk_ffn_down_to_peers).
+// -------------------------------------------------------------------------------------------
+namespace ffnk {
+__global__ void __launch_bounds__(256) sum_row_blocks_kernel(const uint4* __restrict__ blocks, int nblocks,
+                                                             int64_t block_stride16, int64_t ld16, int64_t rows,
+                                                             int chunks, uint4* __restrict__ out, int64_t ldo16) {
+  const int64_t total = rows * chunks;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / chunks;
+    const int c = static_cast<int>(i - r * chunks);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const uint4* src = blocks + r * ld16 + c;
+#pragma unroll 4
+    for (int b = 0; b < nblocks; ++b) {
+      const uint4 v = __ldg(src + b * block_stride16);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += __uint_as_float(w[e] << 16);
+        acc[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+      }
+    }
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+      ow[e] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+    out[r * ldo16 + c] = o;
+  }
+}
+}  // namespace ffnk
+
+extern "C" int ffnk_sum_row_blocks(const void* blocks, int nblocks, int64_t rows, int64_t d, int64_t ldb, void* out,
+                                   int64_t ldo, void* stream) {
+  if (rows == 0) return 0;
+  if (!blocks || !out) return FFNK_ERR_NULL;
+  if (nblocks < 1 || nblocks > 64 || rows < 0 || rows >= (1ll << 30) || d < 8 || (d & 7) || d >= (1ll << 30))
+    return FFNK_ERR_SHAPE;
+  if ((ldb & 7) || (ldo & 7) || ldb < d || ldo < d || (reinterpret_cast<uintptr_t>(blocks) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return FFNK_ERR_ALIGN;
+  const ffnk::DeviceInfo& dev = ffnk::device_info();
+  const int64_t total = rows * (d / 8);
+  int64_t grid = (total + 255) / 256;
+  const int64_t max_grid = static_cast<int64_t>(dev.sm_count) * 8;
+  if (grid > max_grid) grid = max_grid;
+  ffnk::sum_row_blocks_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(blocks), nblocks, rows * (ldb / 8), ldb / 8, rows, static_cast<int>(d / 8),
+      static_cast<uint4*>(out), ldo / 8);
+  return ffnk::cuda_status(cudaGetLastError());
 }
 
 // -------------------------------------------------------------------------------------------

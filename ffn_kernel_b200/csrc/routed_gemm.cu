@@ -63,7 +63,12 @@ enum { A_GATHER = 0, A_ROUTED = 1 };
 //                   (the element-wise terms of the FFN backward, reference README.md:159-172)
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_SWIGLU_SAVE = 2, EPI_DSWIGLU = 3 };
 __host__ __device__ constexpr bool epi_glu(int e) { return e == EPI_SWIGLU || e == EPI_SWIGLU_SAVE; }
-enum { OUT_SCATTER = 0, OUT_ROUTED = 1 };
+// OUT_SCATTER : row of token t -> out[t]            OUT_ROUTED : row i of the routed order -> out[i]
+// OUT_PEER    : row of token t -> row block `peer_rank` of the buffer of the rank that owns token t
+//               (tensor parallel: every rank hands its partial rows straight to their owner)
+enum { OUT_SCATTER = 0, OUT_ROUTED = 1, OUT_PEER = 2 };
+constexpr int MAX_PEERS = 8;
+constexpr int PEER_STAGING = 8 * 4096;   // one 32-row x 128-byte transposition buffer per epilogue warp
 
 struct GemmParams {
   const int* perm;      // routing lists
@@ -89,6 +94,13 @@ struct GemmParams {
   // first A matrix against the first weight, k_len1 columns of a second A matrix (tensor map
   // m[RUN_LEVELS - 1]) against the second weight (the "1" weight maps) go into the same accumulator.
   int k_len1 = 0;
+  // OUT_PEER: peer_out[r] is rank r's buffer of peer_world row blocks, peer_rows rows of ldo elements
+  // each, mapped into this process.  Token t is owned by rank t / peer_rows and lands in row
+  // peer_rank * peer_rows + t % peer_rows of that rank's buffer.
+  __nv_bfloat16* peer_out[MAX_PEERS] = {};
+  int peer_world = 0;
+  int peer_rank = 0;
+  int peer_rows = 1;
 };
 
 // Views of one row-gathered activation matrix: m[0] fetches single rows (gather4); m[1 + i]
@@ -274,6 +286,55 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, const GemmParams& p
         }
       }
     }
+  }
+}
+
+// OUT_PEER: where the row of token `token` goes (nullptr if the token has no owner among the peers).
+__device__ __forceinline__ __nv_bfloat16* peer_row(const GemmParams& p, int token) {
+  const int owner = token / p.peer_rows;
+  if (token < 0 || owner >= p.peer_world) return nullptr;
+  __nv_bfloat16* base = p.peer_out[0];
+#pragma unroll
+  for (int r = 1; r < MAX_PEERS; ++r)
+    if (r == owner) base = p.peer_out[r];
+  const int64_t row = static_cast<int64_t>(p.peer_rank) * p.peer_rows + (token - owner * p.peer_rows);
+  return base + row * p.ldo;
+}
+
+// OUT_PEER epilogue of one warp's 32 accumulator rows.  Rows leave for other GPUs over NVLink, where
+// 16-byte pieces of 32 different rows per instruction would waste most of every packet, so each
+// 64-column chunk goes through a shared-memory transposition (XOR-swizzled 16-byte pieces, conflict
+// free both ways) and is stored as 128 contiguous bytes per row, four rows per instruction.
+// `dst` is this lane's destination row (nullptr: no row), `stg` the warp's 4 KiB staging area.
+template <int BN_T>
+__device__ __forceinline__ void epilogue_rows_peer(uint32_t taddr, const GemmParams& p, __nv_bfloat16* dst, int n_base,
+                                                   int part, int parts, uint8_t* stg, int lane) {
+  constexpr int CH = BN_T / 64;
+  const unsigned long long dptr = reinterpret_cast<unsigned long long>(dst);
+  const int piece = lane & 7;
+#pragma unroll 1
+  for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
+    uint32_t v0[32], v1[32];
+    tmem_ld_32x32(taddr + c * 64, v0);
+    tmem_ld_32x32(taddr + c * 64 + 32, v1);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float a[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] = __uint_as_float(j < 4 ? v0[j * 8 + e] : v1[(j - 4) * 8 + e]);
+      *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = pack_bf16x8(a);
+    }
+    __syncwarp();
+    const int n0 = n_base + c * 64 + piece * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 4 + (lane >> 3);
+      const unsigned long long rp = __shfl_sync(0xFFFFFFFFu, dptr, r);
+      const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128 + ((piece ^ (r & 7)) << 4));
+      if (rp != 0ull && n0 < p.n_out) *reinterpret_cast<uint4*>(rp + static_cast<unsigned long long>(n0) * 2ull) = val;
+    }
+    __syncwarp();
   }
 }
 
@@ -481,8 +542,10 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       const uint32_t acc_phase = (it >> 1) & 1;
       const bool valid = row < tc.rows;
       int64_t dst_row = 0;
+      __nv_bfloat16* peer_dst = nullptr;
       if (valid) {
-        if constexpr (OUT_MODE == OUT_SCATTER) dst_row = p.perm[tc.list_off + tc.row0 + row];
+        if constexpr (OUT_MODE == OUT_PEER) peer_dst = peer_row(p, p.perm[tc.list_off + tc.row0 + row]);
+        else if constexpr (OUT_MODE == OUT_SCATTER) dst_row = p.perm[tc.list_off + tc.row0 + row];
         else dst_row = static_cast<int64_t>(tc.text ? text_row_base(Mv) : 0) + tc.row0 + row;
       }
       int w = 1;
@@ -494,7 +557,11 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN_T;
-      epilogue_row<EPI, BN_T>(taddr, p, dst_row * p.ldo, valid, tc.nt * (epi_glu(EPI) ? BN_T / 2 : BN_T), part, epilogue_parts());
+      if constexpr (OUT_MODE == OUT_PEER)
+        epilogue_rows_peer<BN_T>(taddr, p, peer_dst, tc.nt * BN_T, part, epilogue_parts(),
+                                 smem + TSTAGES * TSTAGE_BYTES + 256 + (warp - 2) * 4096, lane);
+      else
+        epilogue_row<EPI, BN_T>(taddr, p, dst_row * p.ldo, valid, tc.nt * (epi_glu(EPI) ? BN_T / 2 : BN_T), part, epilogue_parts());
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -751,8 +818,10 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       const uint32_t acc_phase = (it >> 1) & 1;
       const bool valid = row < tc.rows;
       int64_t dst_row = 0;
+      __nv_bfloat16* peer_dst = nullptr;
       if (valid) {
-        if constexpr (OUT_MODE == OUT_SCATTER) dst_row = p.perm[tc.list_off + tc.row0 + row];
+        if constexpr (OUT_MODE == OUT_PEER) peer_dst = peer_row(p, p.perm[tc.list_off + tc.row0 + row]);
+        else if constexpr (OUT_MODE == OUT_SCATTER) dst_row = p.perm[tc.list_off + tc.row0 + row];
         else dst_row = static_cast<int64_t>(tc.text ? text_base : 0) + tc.row0 + row;
       }
       int w = 1;
@@ -766,7 +835,11 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      epilogue_row<EPI, BN>(taddr, p, dst_row * p.ldo, valid, tc.nt * N_PER_TILE, part, epilogue_parts());
+      if constexpr (OUT_MODE == OUT_PEER)
+        epilogue_rows_peer<BN>(taddr, p, peer_dst, tc.nt * N_PER_TILE, part, epilogue_parts(),
+                               smem + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * 4096, lane);
+      else
+        epilogue_row<EPI, BN>(taddr, p, dst_row * p.ldo, valid, tc.nt * N_PER_TILE, part, epilogue_parts());
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
@@ -1186,17 +1259,18 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
   const int n_per_tile = epi_glu(EPI) ? tile.bn / 2 : tile.bn;
   const int64_t n_tiles = (p.n_out + n_per_tile - 1) / n_per_tile;
+  constexpr int extra_smem = OUT_MODE == OUT_PEER ? PEER_STAGING : 0;
   if (tile.pair) {
     int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
     if (pairs > usable_sms(dev) / 2) pairs = usable_sms(dev) / 2;
     if (pairs < 1) pairs = 1;
     auto go = [&](auto kernel) -> int {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM + extra_smem);
       if (e != cudaSuccess) return cuda_status(e);
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
       cfg.blockDim = dim3(gemm_threads_for(static_cast<int64_t>(p.k_len) + p.k_len1));
-      cfg.dynamicSmemBytes = PAIR_SMEM;
+      cfg.dynamicSmemBytes = PAIR_SMEM + extra_smem;
       cfg.stream = stream;
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1214,9 +1288,9 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   if (grid > usable_sms(dev)) grid = usable_sms(dev);
   if (grid < 1) grid = 1;
   auto go = [&](auto kernel) -> int {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM + extra_smem);
     if (e != cudaSuccess) return cuda_status(e);
-    kernel<<<static_cast<unsigned>(grid), gemm_threads_for(static_cast<int64_t>(p.k_len) + p.k_len1), GEMM_SMEM, stream>>>(
+    kernel<<<static_cast<unsigned>(grid), gemm_threads_for(static_cast<int64_t>(p.k_len) + p.k_len1), GEMM_SMEM + extra_smem, stream>>>(
         tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
     return cuda_status(cudaGetLastError());
   };
@@ -1366,6 +1440,44 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(y), ldy, static_cast<int>(d), static_cast<int>(h),
                static_cast<int>(M), pick_group_m(h), max_run_rows(), status, g_prof_buffer};
   return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ffnk_ffn_down_to_peers(const void* inter, int64_t ldi, const void* w2, const void* u2,
+                                      int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm,
+                                      const int32_t* counts, void* const* peer_blocks, int world, int rank,
+                                      int64_t rows_per_rank, int64_t ldb, int64_t M, int64_t d, int64_t h,
+                                      int32_t* status, void* stream) {
+  if (M == 0) return 0;
+  if (!inter || !w2 || !u2 || !perm || !counts || !peer_blocks) return FFNK_ERR_NULL;
+  if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
+  if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world || rows_per_rank < 1 ||
+      rows_per_rank * world < M || rows_per_rank * world >= (1ll << 30))
+    return FFNK_ERR_SHAPE;
+  if ((ldi & 7) || (ldb & 7) || ldi < h || ldb < d) return FFNK_ERR_ALIGN;
+  for (int r = 0; r < world; ++r) {
+    if (!peer_blocks[r]) return FFNK_ERR_NULL;
+    if (reinterpret_cast<uintptr_t>(peer_blocks[r]) & 15) return FFNK_ERR_ALIGN;
+  }
+  const int64_t rows = ffnk_route_capacity(M) + 512;
+  AMaps tmA;
+  CUtensorMap tmB[4];
+  int r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], inter, h, rows, ldi, BK, BM);
+  if (r) return r;
+  for (int i = 0; i <= COPY_MAP; ++i)
+    if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
+  bool mn1 = false, mn2 = false;
+  const TileChoice tile = pick_tile(M, d, A_ROUTED, EPI_STORE, weights_k_major(w_stride_k, w_stride_n, h));
+  if ((r = weight_map(&tmB[0], WeightView{w2, w_stride_k, w_stride_n, h, d}, &mn1, tile.bn / 2))) return r;
+  if ((r = weight_map(&tmB[2], WeightView{u2, w_stride_k, w_stride_n, h, d}, &mn2, tile.bn / 2))) return r;
+  tmB[1] = tmB[0];
+  tmB[3] = tmB[2];
+  GemmParams p{perm, counts, nullptr, ldb, static_cast<int>(d), static_cast<int>(h),
+               static_cast<int>(M), pick_group_m(h), max_run_rows(), status, g_prof_buffer};
+  for (int i = 0; i < world; ++i) p.peer_out[i] = static_cast<__nv_bfloat16*>(peer_blocks[i]);
+  p.peer_world = world;
+  p.peer_rank = rank;
+  p.peer_rows = static_cast<int>(rows_per_rank);
+  return launch_gemm<A_ROUTED, EPI_STORE, OUT_PEER>(tmA, tmB, mn1, p, M, tile, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,

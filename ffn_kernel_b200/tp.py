@@ -152,3 +152,118 @@ def all_reduce_gradients(tensors: Sequence[torch.Tensor], group=None, bucket_byt
         if size >= bucket_bytes:
             flush()
     flush()
+
+
+class PeerBlocks:
+    """Per-rank block buffers, mapped into every rank, for ``masked_ffn_tp_fused``.
+
+    Rank ``r`` owns tokens ``[r * rows, (r + 1) * rows)`` with ``rows = ceil(M / world)``.  Its buffer
+    holds ``world`` row blocks of ``rows x d`` bf16; block ``s`` receives rank ``s``'s partial result
+    for the owner's rows.  Two buffers alternate from call to call, so the writes of step ``k + 1``
+    never touch what an owner may still be summing from step ``k`` (one barrier per step is
+    enough).  Construction is collective: every rank of ``group`` must create it, in the same order.
+    """
+
+    def __init__(self, M: int, d: int, group=None, device=None, buffers: int = 2):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        if not dist.is_initialized():
+            raise RuntimeError("PeerBlocks needs an initialised torch.distributed process group")
+        group = group or dist.group.WORLD
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one NVLink domain)")
+        if d % 8:
+            raise ValueError("d must be a multiple of 8")
+        self.M, self.d = M, d
+        self.rows = max(1, -(-M // self.world))
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.device = device
+        self.buffers, self.pointers, self._handles = [], [], []
+        for _ in range(buffers):
+            t = symm.empty(self.world * self.rows * d, dtype=torch.bfloat16, device=device)
+            hdl = symm.rendezvous(t, group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            if len(ptrs) != self.world or ptrs[self.rank] != t.data_ptr():
+                raise RuntimeError("symmetric memory rendezvous returned unexpected buffer pointers")
+            self.buffers.append(t.view(self.world * self.rows, d))
+            self.pointers.append((ctypes.c_void_p * self.world)(*ptrs))
+            self._handles.append(hdl)
+        self._turn = 0
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def next(self):
+        i = self._turn
+        self._turn = (i + 1) % len(self.buffers)
+        return self.buffers[i], self.pointers[i]
+
+    def barrier(self) -> None:
+        """Stream-ordered barrier: returns (on the stream) once every rank's earlier work on its
+        stream has completed.  A one-element all-reduce: its kernel on each rank starts after that
+        rank's earlier kernels and cannot finish before all ranks have contributed."""
+        dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group)
+
+    def owned_rows(self) -> slice:
+        return slice(min(self.M, self.rank * self.rows), min(self.M, (self.rank + 1) * self.rows))
+
+
+def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gather: bool = True):
+    """Tensor-parallel MaskedFFN forward whose down projection writes its partial rows straight
+    into the memory of the rank that owns them (NVLink peer stores from the GEMM epilogue,
+    ``ffnk_ffn_down_to_peers``), followed by one barrier and a local fp32 sum of the ``world``
+    partials (``ffnk_sum_row_blocks``).  The partial ``y`` never exists in this rank's memory and
+    no reduction collective runs.
+
+    ``gather=True`` returns the full ``y`` on every rank (one all-gather of the owned rows);
+    ``gather=False`` returns ``(rows, y[rows])`` with ``rows = blocks.owned_rows()``.
+    The weights are this rank's shards (``shard_ffn_weights``); ``x`` and ``mask`` are replicated."""
+    from ._lib import check, lib
+    from .ffn import permute_rows_first
+    from .linear import _activation, _check_dims, _mask_route, _weights
+    from .route import maybe_check, status_word, stream_ptr
+
+    x = _activation(x, "x")
+    M, d = x.shape
+    h = w1.shape[1] if isinstance(w1, torch.Tensor) and w1.dim() == 2 else -1
+    w1, w3, u1, u3 = _weights((w1, w3, u1, u3), ("w1", "w3", "u1", "u3"), d, h)
+    w2, u2 = _weights((w2, u2), ("w2", "u2"), h, d)
+    _check_dims(d=d, h=h)
+    if (M, d) != (blocks.M, blocks.d) or x.device != blocks.device:
+        raise RuntimeError(f"PeerBlocks were made for [{blocks.M}, {blocks.d}] on {blocks.device}")
+    dev = x.device
+    L = lib()
+    world, rank, rows = blocks.world, blocks.rank, blocks.rows
+    with torch.cuda.device(dev):
+        st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
+        own = torch.empty((rows, d), device=dev, dtype=torch.bfloat16)
+        if M > 0:
+            rt = _mask_route(mask, M, dev, None)
+            inter = torch.empty((rt.cap + 512, h), device=dev, dtype=torch.bfloat16)
+            xin, routed_in = x, 0
+            if permute_rows_first(M, d, h):
+                xin = torch.empty((rt.cap + 512, d), device=dev, dtype=torch.bfloat16)
+                check("ffnk_permute_rows", L.ffnk_permute_rows(
+                    x.data_ptr(), x.stride(0), rt.perm.data_ptr(), rt.counts.data_ptr(), xin.data_ptr(),
+                    xin.stride(0), M, d, sp))
+                routed_in = 1
+            check("ffnk_ffn_gateup", L.ffnk_ffn_gateup(
+                xin.data_ptr(), xin.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),
+                w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(),
+                inter.stride(0), routed_in, 1, M, d, h, st, sp))
+            buf, ptrs = blocks.next()
+            check("ffnk_ffn_down_to_peers", L.ffnk_ffn_down_to_peers(
+                inter.data_ptr(), inter.stride(0), w2.data_ptr(), u2.data_ptr(), w2.stride(0), w2.stride(1),
+                rt.perm.data_ptr(), rt.counts.data_ptr(), ptrs, world, rank, rows, d, M, d, h, st, sp))
+            blocks.barrier()
+            check("ffnk_sum_row_blocks", L.ffnk_sum_row_blocks(buf.data_ptr(), world, rows, d, d, own.data_ptr(), d, sp))
+        maybe_check(dev)
+        if not gather:
+            r = blocks.owned_rows()
+            return r, own[: r.stop - r.start]
+        y = torch.empty((world * rows, d), device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(y, own, group=blocks.group)
+        return y[:M]

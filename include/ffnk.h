@@ -151,6 +151,37 @@ int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2
                   int64_t d, int64_t h, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Tensor parallel over h: down projection fused with the first half of a reduce-scatter.
+ * The reference is single-device (test_linear.py:74 selects device 0); this has no counterpart
+ * there.  Each of `world` ranks holds h / world columns of the intermediate and the matching rows
+ * of w2/u2, so its down projection is a partial sum of every output row.  Token t is owned by
+ * rank t / rows_per_rank.  Instead of writing its partial y and handing it to a collective, the
+ * GEMM's epilogue stores each partial row directly into the owner's memory over NVLink:
+ *     peer_blocks[t / rows_per_rank][(rank * rows_per_rank + t % rows_per_rank) * ldb + c]
+ *         = partial y[t, c]
+ * peer_blocks is a HOST array of `world` device pointers (1 <= world <= 8): entry r is rank r's
+ * block buffer, bf16 [world * rows_per_rank, ldb], mapped into this process (CUDA IPC, a
+ * symmetric-memory allocation, or cudaMalloc'd memory of a peer-enabled device in the same
+ * process); entry `rank` is this rank's own buffer.  rows_per_rank * world >= M.
+ * The call does not wait for or signal other ranks: the caller orders it after every owner has
+ * finished reading the previous contents of its buffer, and orders ffnk_sum_row_blocks on each
+ * owner after all ranks' calls have completed (a stream-ordered barrier between the two).
+ * ------------------------------------------------------------------------------------- */
+int ffnk_ffn_down_to_peers(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
+                           int64_t w_stride_n, const int32_t* perm, const int32_t* counts,
+                           void* const* peer_blocks, int world, int rank, int64_t rows_per_rank, int64_t ldb,
+                           int64_t M, int64_t d, int64_t h, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Second half of that reduce-scatter, run by the owner on its own buffer:
+ *     out[r, c] = bf16( sum over b < nblocks of fp32(blocks[(b * rows + r) * ldb + c]) )
+ * blocks bf16 [nblocks * rows, ldb]; out bf16 [rows, ldo]; d columns, d % 8 == 0.
+ * No counterpart in the reference.
+ * ------------------------------------------------------------------------------------- */
+int ffnk_sum_row_blocks(const void* blocks, int nblocks, int64_t rows, int64_t d, int64_t ldb, void* out,
+                        int64_t ldo, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Small-M (decode) MaskedFFN forward: streams each present modality's weights once with
  * 128-bit loads; same contract as MaskedFFN.forward (ffn_kernel/ops.py:28-32).
  * inter: scratch bf16 [M, h].  Supported for M <= ffnk_decode_max_tokens() (32) and K-major weights.

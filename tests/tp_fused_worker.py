@@ -1,0 +1,94 @@
+"""One rank of the multi-GPU check of ``masked_ffn_tp_fused`` (run under torch.distributed.run by
+``test_gpu_tp_fused.py``; not collected by pytest).  Every rank computes the tensor-parallel
+MaskedFFN three ways -- fused peer stores with and without the final all-gather, and partial
+outputs summed by an NCCL all-reduce -- and rank 0 compares them with the fp32 oracle.  With
+``--time`` it also prints device timings of the variants."""
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ffn_kernel_b200 import check_status, tp  # noqa: E402
+from ffn_kernel_b200.synth import edge_mask, ffn_case  # noqa: E402
+
+
+def timed(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / steps], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--M", type=int, default=1000)
+    ap.add_argument("--d", type=int, default=256)
+    ap.add_argument("--h", type=int, default=960)
+    ap.add_argument("--mask", default="span")
+    ap.add_argument("--time", action="store_true")
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--no-oracle", action="store_true")
+    args = ap.parse_args()
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    c = ffn_case(args.M, args.d, args.h, seed=3, mask=edge_mask(args.M, args.mask, seed=7))
+    g = c.to(dev)
+    x, mask = g.x, g.mask
+    shards = tp.shard_ffn_weights(*g.apply_args()[1:7], rank, world)
+    blocks = tp.PeerBlocks(args.M, args.d)
+
+    out = {}
+    for rep in range(3):                       # repeated calls alternate the two block buffers
+        y_fused = tp.masked_ffn_tp_fused(x, *shards, mask, blocks)
+    rows, y_own = tp.masked_ffn_tp_fused(x, *shards, mask, blocks, gather=False)
+    y_nccl = tp.masked_ffn_tp(x, *shards, mask)
+    torch.cuda.synchronize()
+    check_status()
+    out["fused_vs_nccl"] = float((y_fused.float() - y_nccl.float()).abs().max() / y_nccl.float().abs().max())
+    out["own_rows_equal"] = bool(torch.equal(y_own, y_fused[rows]))
+    same = torch.tensor([1.0 if out["own_rows_equal"] else 0.0], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    out["own_rows_equal"] = bool(same.item() == 1.0)
+    if not args.no_oracle and rank == 0:
+        from oracle import masked_ref as O
+        ref = O.masked_ffn(*c.apply_args())
+        out["fused_vs_oracle"] = float(O.max_rel_err(y_fused, ref))
+        out["nccl_vs_oracle"] = float(O.max_rel_err(y_nccl, ref))
+    if args.time:
+        flops = 6.0 * args.M * args.d * args.h
+        for name, fn in (("fused_allgather", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks)),
+                         ("fused_row_sharded", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, gather=False)),
+                         ("nccl_all_reduce", lambda: tp.masked_ffn_tp(x, *shards, mask)),
+                         ("nccl_reduce_scatter", (lambda: tp.masked_ffn_tp_reduce_scatter(x, *shards, mask))
+                          if args.M % world == 0 else None)):
+            if fn is None:
+                continue
+            ms = timed(fn, args.steps, 5)
+            out[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+        check_status()
+    if rank == 0:
+        out.update(world=world, M=args.M, d=args.d, h=args.h, mask=args.mask)
+        print("TP_FUSED " + json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
