@@ -16,8 +16,10 @@ N > 1 shards the tokens by default (``--mode dp``: every rank routes and multipl
 with replicated weights, no data-path collective, weak scaling) -- the tokens are independent
 units, so this is how the path partitions.  The same run then also times the tensor-parallel
 mode (weights sharded over h, partial outputs summed by NCCL all-reduce in token chunks, total
-work fixed) and reports it under ``"tp"``; ``--mode tp`` makes that the headline instead
-(strong scaling).
+work fixed) and reports it under ``"tp"``, together with (``"tp"."fused"``) the variant whose
+down projection stores its partial rows straight into their owner's memory over NVLink instead of
+handing a partial output to a collective; ``--mode tp`` makes the NCCL variant the headline
+instead (strong scaling).
 """
 from __future__ import annotations
 
@@ -331,23 +333,40 @@ def run_ours(args):
         m_tp = m8.bool()
         w_tp = tp.shard_ffn_weights(*full_args[1:7], rank, world)      # views of the replicated weights
         tp_steps = max(3, min(args.steps, 10))
-        for _ in range(3):
-            tp.masked_ffn_tp(x_tp, *w_tp, m_tp, chunks=args.chunks)
-        barrier()
-        t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0e.record()
-        for _ in range(tp_steps):
-            tp.masked_ffn_tp(x_tp, *w_tp, m_tp, chunks=args.chunks)
-        t1e.record()
-        barrier()
-        t = torch.tensor([t0e.elapsed_time(t1e)], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        tp_ms = float(t.item()) / tp_steps
-        check_status()
-        tp_line = {"value": 6.0 * M * d * h / (tp_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": tp_ms,
-                   "steps": tp_steps, "scaling": "strong", "chunks": args.chunks,
-                   "collective": "NCCL all-reduce of the partial outputs, one per token chunk",
-                   "tokens_per_s": M / (tp_ms * 1e-3)}
+
+        def time_tp(fn):
+            for _ in range(3):
+                fn()
+            barrier()
+            t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0e.record()
+            for _ in range(tp_steps):
+                fn()
+            t1e.record()
+            barrier()
+            t = torch.tensor([t0e.elapsed_time(t1e)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            check_status()
+            ms = float(t.item()) / tp_steps
+            return {"value": 6.0 * M * d * h / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+                    "tokens_per_s": M / (ms * 1e-3)}
+
+        tp_line = time_tp(lambda: tp.masked_ffn_tp(x_tp, *w_tp, m_tp, chunks=args.chunks))
+        tp_line.update(steps=tp_steps, scaling="strong", chunks=args.chunks,
+                       collective="NCCL all-reduce of the partial outputs, one per token chunk")
+        # the same step with the reduce-scatter folded into the down projection (peer stores over NVLink)
+        try:
+            blocks = tp.PeerBlocks(M, d)
+        except Exception as exc:                      # symmetric memory not available on this box
+            tp_line["fused"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+        else:
+            fused = time_tp(lambda: tp.masked_ffn_tp_fused(x_tp, *w_tp, m_tp, blocks))
+            fused["collective"] = ("down-projection epilogue stores partial rows into their owner's memory; "
+                                   "one barrier, local fp32 sum, NCCL all-gather of the owned rows")
+            fused["row_sharded_output"] = time_tp(
+                lambda: tp.masked_ffn_tp_fused(x_tp, *w_tp, m_tp, blocks, gather=False))
+            tp_line["fused"] = fused
+            del blocks
         del w_tp, x_tp
 
     # ---- CPU baseline (rank 0, single GPU only) -------------------------------------------------

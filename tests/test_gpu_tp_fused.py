@@ -37,7 +37,7 @@ def _run(nproc, *worker_args, timeout=600):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("M,d,h,mask", [(1000, 256, 960, "span"), (4100, 512, 1344, "bernoulli")])
 def test_two_ranks(M, d, h, mask):
-    out = _run(2, "--M", str(M), "--d", str(d), "--h", str(h), "--mask", mask)
+    out = _run(2, "--tokens", str(M), "--dim", str(d), "--hidden", str(h), "--mask-kind", mask)
     assert out["world"] == 2
     assert out["own_rows_equal"]
     assert out["fused_vs_oracle"] < TOL

@@ -35,10 +35,10 @@ def timed(fn, steps, warmup):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--M", type=int, default=1000)
-    ap.add_argument("--d", type=int, default=256)
-    ap.add_argument("--h", type=int, default=960)
-    ap.add_argument("--mask", default="span")
+    ap.add_argument("--tokens", type=int, default=1000)
+    ap.add_argument("--dim", type=int, default=256)
+    ap.add_argument("--hidden", type=int, default=960)
+    ap.add_argument("--mask-kind", default="span")
     ap.add_argument("--time", action="store_true")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--no-oracle", action="store_true")
@@ -48,11 +48,11 @@ def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
-    c = ffn_case(args.M, args.d, args.h, seed=3, mask=edge_mask(args.M, args.mask, seed=7))
+    c = ffn_case(args.tokens, args.dim, args.hidden, seed=3, mask=edge_mask(args.tokens, args.mask_kind, seed=7))
     g = c.to(dev)
     x, mask = g.x, g.mask
     shards = tp.shard_ffn_weights(*g.apply_args()[1:7], rank, world)
-    blocks = tp.PeerBlocks(args.M, args.d)
+    blocks = tp.PeerBlocks(args.tokens, args.dim)
 
     out = {}
     for rep in range(3):                       # repeated calls alternate the two block buffers
@@ -72,19 +72,19 @@ def main():
         out["fused_vs_oracle"] = float(O.max_rel_err(y_fused, ref))
         out["nccl_vs_oracle"] = float(O.max_rel_err(y_nccl, ref))
     if args.time:
-        flops = 6.0 * args.M * args.d * args.h
+        flops = 6.0 * args.tokens * args.dim * args.hidden
         for name, fn in (("fused_allgather", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks)),
                          ("fused_row_sharded", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, gather=False)),
                          ("nccl_all_reduce", lambda: tp.masked_ffn_tp(x, *shards, mask)),
                          ("nccl_reduce_scatter", (lambda: tp.masked_ffn_tp_reduce_scatter(x, *shards, mask))
-                          if args.M % world == 0 else None)):
+                          if args.tokens % world == 0 else None)):
             if fn is None:
                 continue
             ms = timed(fn, args.steps, 5)
             out[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
         check_status()
     if rank == 0:
-        out.update(world=world, M=args.M, d=args.d, h=args.h, mask=args.mask)
+        out.update(world=world, M=args.tokens, d=args.dim, h=args.hidden, mask=args.mask_kind)
         print("TP_FUSED " + json.dumps(out), flush=True)
     dist.barrier()
     dist.destroy_process_group()
