@@ -887,6 +887,7 @@ struct WgradParams {
                     //    whenever the mask's average run is shorter than this (decided on the device);
                     //    their height is copy_rows
   int copy_rows = 0;
+  long long* prof = nullptr;   // optional per-CTA wait-cycle counters (8 per CTA), as in GemmParams
 };
 
 // Views of one operand of the weight-gradient GEMM: m[0] single rows (gather4), m[1 + i] boxes of
@@ -975,6 +976,7 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
     const int pad_row = use_copies ? p.copy_rows : p.pad_row;
     const int gi = lane & 15;     // which group of four list rows inside the k-step
     const int half = lane >> 4;   // which 64-column block (of a pair)
+    long long t_begin = clock64(), t_wait = 0;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const WgradTile wt = decode_wgrad_tile(t, p_tiles, q_tiles, Mv, Mt, cap);
       if (wt.cnt == 0) continue;
@@ -984,6 +986,32 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
       const int group_base = wt.text ? text_row_base(Mv) : 0;
       int4 nxt = (!routed && 4 * gi < wt.cnt) ? *reinterpret_cast<const int4*>(list + 4 * gi) : pad4;
       for (int ks = 0; ks < k_steps; ++ks) {
+        if (routed && (ks + 1) * BK <= wt.cnt) {
+          // 64 whole rows of a routed-order matrix: six boxes, one lane each, nothing to detect.
+          // (The instruction count of this loop is what the MMA issuer ends up waiting for.)
+          int w = 1;
+          const long long tw = clock64();
+          if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
+          w = __shfl_sync(0xFFFFFFFFu, w, 0);
+          t_wait += clock64() - tw;
+          if (!w) {
+            if (lane == 0) report(p.status, ST_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* sp = smem + stage * STAGE_BYTES;
+          if (lane == 0) mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
+          __syncwarp();
+          if (lane < 6) {
+            const bool is_p = lane < 2;
+            const int b = is_p ? lane : lane - 2;
+            tma_load_2d((is_p ? sp : sp + A_BYTES) + b * 8192, is_p ? &mp->m[RUN_LEVELS - 1] : &mq->m[RUN_LEVELS - 1],
+                        &full[stage], (is_p ? wt.pt * BM : wt.qt * BN) + b * 64, group_base + ks * BK);
+          }
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          continue;
+        }
         const int lr = ks * BK + 4 * gi;
         int4 v = nxt;
         if (routed) {
@@ -1005,8 +1033,10 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
         const bool run_lead = run_lanes > 0 && (gi & (run_lanes - 1)) == 0;
         const int level = run_lanes > 0 ? 32 - __clz(run_lanes) : 0;
         int w = 1;
+        const long long tw = clock64();
         if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
         w = __shfl_sync(0xFFFFFFFFu, w, 0);
+        t_wait += clock64() - tw;
         if (!w) {
           if (lane == 0) report(p.status, ST_TIMEOUT_PRODUCER);
           ok = false;
@@ -1034,6 +1064,10 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
+    if (p.prof && lane == 0) {
+      p.prof[blockIdx.x * 8 + 3] = t_wait;
+      p.prof[blockIdx.x * 8 + 4] = clock64() - t_begin;
+    }
     if (*abort_flag && lane == 0) {
       int s = stage;
       uint32_t ph = phase;
@@ -1052,6 +1086,7 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      long long t_begin = clock64(), t_full = 0, t_tmem = 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const WgradTile wt = decode_wgrad_tile(t, p_tiles, q_tiles, Mv, Mt, cap);
         if (wt.cnt == 0) continue;
@@ -1059,18 +1094,22 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ++it;
+        long long tw = clock64();
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
           report(p.status, ST_TIMEOUT_MMA_TMEM);
           break;
         }
+        t_tmem += clock64() - tw;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int ks = 0; ks < k_steps; ++ks) {
+          tw = clock64();
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             report(p.status, ST_TIMEOUT_MMA_FULL);
             ok = false;
             break;
           }
+          t_full += clock64() - tw;
           tc_fence_after();
           const uint32_t p_addr = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t q_addr = p_addr + A_BYTES;
@@ -1084,6 +1123,12 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tfull[acc]);
+      }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = clock64() - t_begin;
+        p.prof[blockIdx.x * 8 + 1] = t_full;
+        p.prof[blockIdx.x * 8 + 2] = t_tmem;
+        p.prof[blockIdx.x * 8 + 7] = it;
       }
     }
     __syncwarp();
@@ -1150,6 +1195,238 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+// -------------------------------------------------------------------------------------------
+// Weight gradient on CTA pairs: operands in routed order only (the FFN backward's matrices, or the
+// routed-order copies the MaskedLinear backward makes).  One 256 x 256 output tile per pair; each
+// CTA fetches its own 128 columns of P and only its half of the 256 columns of Q, i.e. four boxes
+// of 64 rows x 64 columns per k-step instead of the single-CTA kernel's six, 32 KiB instead of
+// 48 KiB, six pipeline stages instead of four.  (In the single-CTA kernel the MMA issuer spends
+// 40-50 % of its time waiting for operands; the TMA requests per k-step are what it waits for.)
+// The last k-step of a modality, when it is not 64 whole rows, is fetched row by row (gather4)
+// with the missing rows pointed at an out-of-range row, which the TMA unit fills with zeros.
+// -------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(GEMM_THREADS_MAX, 1)
+wgrad_pair_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm, const WgradParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES);
+  uint64_t* empty = full + PAIR_STAGES;
+  uint64_t* tfull = empty + PAIR_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full[s], 2);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 8 * epilogue_parts());
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&pm.m[0]);
+    tma_prefetch_desc(&qm.m[0]);
+    tma_prefetch_desc(&pm.m[RUN_LEVELS - 1]);
+    tma_prefetch_desc(&qm.m[RUN_LEVELS - 1]);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, TMEM_COLS);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int Mv = p.counts[0], Mt = p.counts[1], cap = p.counts[2];
+  const int p_tiles = (p.p_dim + PAIR_BM - 1) / PAIR_BM;
+  const int q_tiles = (p.q_dim + BN - 1) / BN;
+  const int total_tiles = 2 * p_tiles * q_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (both CTAs)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    long long t_begin = clock64(), t_wait = 0;
+    for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
+      const WgradTile wt = decode_wgrad_tile(t, p_tiles, q_tiles, Mv, Mt, cap);
+      if (wt.cnt == 0) continue;
+      const int k_steps = (wt.cnt + BK - 1) / BK;
+      const int group_base = wt.text ? text_row_base(Mv) : 0;
+      // lanes 0,1: this CTA's two 64-column blocks of P; lanes 2,3: its two blocks of Q
+      const bool is_p = (lane & 2) == 0;
+      const int blk = lane & 1;
+      const int col = (is_p ? wt.pt * PAIR_BM : wt.qt * BN) + static_cast<int>(rank) * BM + blk * 64;
+      const int dst_off = (is_p ? 0 : A_BYTES) + blk * 8192;
+      for (int ks = 0; ks < k_steps; ++ks) {
+        int w = 1;
+        const long long tw = clock64();
+        if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
+        w = __shfl_sync(0xFFFFFFFFu, w, 0);
+        t_wait += clock64() - tw;
+        if (!w) {
+          if (lane == 0) report(p.status, ST_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        uint8_t* st = smem + stage * PAIR_STAGE_BYTES;
+        const uint32_t lead_full = mapa_shared(smem_u32(&full[stage]), 0);
+        if (lane == 0) mbar_arrive_expect_tx_cluster(lead_full, PAIR_STAGE_BYTES);
+        __syncwarp();
+        if ((ks + 1) * BK <= wt.cnt) {
+          if (lane < 4)
+            tma_load_2d_pair(st + dst_off, is_p ? &pm.m[RUN_LEVELS - 1] : &qm.m[RUN_LEVELS - 1], lead_full, col,
+                             group_base + ks * BK);
+        } else if (lane < 16) {
+          // ragged end of the modality: lane g fetches rows 4g..4g+3 of the k-step for all four blocks
+          const int lr = ks * BK + 4 * lane;
+          const int r0 = lr + 0 < wt.cnt ? group_base + lr + 0 : p.pad_row;
+          const int r1 = lr + 1 < wt.cnt ? group_base + lr + 1 : p.pad_row;
+          const int r2 = lr + 2 < wt.cnt ? group_base + lr + 2 : p.pad_row;
+          const int r3 = lr + 3 < wt.cnt ? group_base + lr + 3 : p.pad_row;
+          const int cp = wt.pt * PAIR_BM + static_cast<int>(rank) * BM;
+          const int cq = wt.qt * BN + static_cast<int>(rank) * BM;
+          tma_gather4_pair(st + lane * 512, &pm.m[0], lead_full, cp, r0, r1, r2, r3);
+          tma_gather4_pair(st + 8192 + lane * 512, &pm.m[0], lead_full, cp + 64, r0, r1, r2, r3);
+          tma_gather4_pair(st + A_BYTES + lane * 512, &qm.m[0], lead_full, cq, r0, r1, r2, r3);
+          tma_gather4_pair(st + A_BYTES + 8192 + lane * 512, &qm.m[0], lead_full, cq + 64, r0, r1, r2, r3);
+        }
+        if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (p.prof && lane == 0) {
+      p.prof[blockIdx.x * 8 + 3] = t_wait;
+      p.prof[blockIdx.x * 8 + 4] = clock64() - t_begin;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(PAIR_BM, BN, true, true);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      long long t_begin = clock64(), t_full = 0, t_tmem = 0;
+      for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
+        const WgradTile wt = decode_wgrad_tile(t, p_tiles, q_tiles, Mv, Mt, cap);
+        if (wt.cnt == 0) continue;
+        const int k_steps = (wt.cnt + BK - 1) / BK;
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
+        long long tw = clock64();
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+          report(p.status, ST_TIMEOUT_MMA_TMEM);
+          break;
+        }
+        t_tmem += clock64() - tw;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int ks = 0; ks < k_steps; ++ks) {
+          tw = clock64();
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            report(p.status, ST_TIMEOUT_MMA_FULL);
+            ok = false;
+            break;
+          }
+          t_full += clock64() - tw;
+          tc_fence_after();
+          const uint32_t p_addr = smem_u32(smem + stage * PAIR_STAGE_BYTES);
+          const uint32_t q_addr = p_addr + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t dp = umma_smem_desc(p_addr + kk * (UMMA_K * 128), 8192, 1024);
+            const uint64_t dq = umma_smem_desc(q_addr + kk * (UMMA_K * 128), 8192, 1024);
+            umma_bf16<2>(tmem_d, dp, dq, idesc, (ks | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage], 3);
+          if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tfull[acc], 3);
+      }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = clock64() - t_begin;
+        p.prof[blockIdx.x * 8 + 1] = t_full;
+        p.prof[blockIdx.x * 8 + 2] = t_tmem;
+        p.prof[blockIdx.x * 8 + 7] = it;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    const int part = (warp - 2) >> 2;
+    const int row = q * 32 + lane;
+    int it = 0;
+    for (int t = pair_id; t < total_tiles; t += num_pairs) {
+      const WgradTile wt = decode_wgrad_tile(t, p_tiles, q_tiles, Mv, Mt, cap);
+      const int prow = wt.pt * PAIR_BM + static_cast<int>(rank) * BM + row;
+      const bool valid = prow < p.p_dim;
+      __nv_bfloat16* out_row = (wt.text ? p.out_t : p.out_v) + static_cast<int64_t>(prow) * p.ldo;
+      const int q_base = wt.qt * BN;
+      if (wt.cnt == 0) {
+        if (valid) {
+          for (int c = part * (BN / epilogue_parts()); c < (part + 1) * (BN / epilogue_parts()); c += 8)
+            if (q_base + c < p.q_dim) *reinterpret_cast<uint4*>(out_row + q_base + c) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
+      int w = 1;
+      if (lane == 0) w = mbar_wait(&tfull[acc], acc_phase, abort_flag) ? 1 : 0;
+      w = __shfl_sync(0xFFFFFFFFu, w, 0);
+      if (!w) {
+        if (lane == 0) report(p.status, ST_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = part * (BN / 32) / epilogue_parts(); c < (part + 1) * (BN / 32) / epilogue_parts(); ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int n0 = q_base + c * 32;
+        if (valid && n0 < p.q_dim) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (n0 + j * 8 < p.q_dim) {
+              float a[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) a[e] = __uint_as_float(v[j * 8 + e]);
+              *reinterpret_cast<uint4*>(out_row + n0 + j * 8) = pack_bf16x8(a);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<2>(tmem_base, TMEM_COLS);
   }
 }
 
@@ -1305,6 +1582,8 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
 // Average run length below which a routed-order copy beats gathering rows inside a GEMM with
 // `columns` output columns (see mask_is_scattered).
 static int copy_threshold(int64_t columns) {
+  static const int forced = env_flag("FFNK_COPY_THRESHOLD");   // experiments: run length below which copies are made
+  if (forced >= 0) return forced;
   const int64_t t = columns / 6;
   return static_cast<int>(t < 32 ? 32 : (t > 4096 ? 4096 : t));
 }
@@ -1336,6 +1615,31 @@ static int launch_wgrad(const void* P, int64_t ldp, int64_t p_dim, const void* Q
                  static_cast<int>(p_dim), static_cast<int>(q_dim), static_cast<int>(rows_total),
                  max_run_rows() < 64 ? max_run_rows() : 64, status, routed, copies ? copy_thr : 0,
                  static_cast<int>(copy_rows)};
+  wp.prof = g_prof_buffer;
+  // operands in routed order and an output big enough for 256 x 256 tiles: the CTA-pair kernel
+  // (FFNK_WGRAD_PAIR=0/1 overrides for experiments)
+  static const int force_pair = env_flag("FFNK_WGRAD_PAIR");
+  const bool pair_ok = routed != 0;
+  const bool pair = pair_ok && (force_pair >= 0 ? force_pair != 0 : (p_dim >= 256 && q_dim >= 128 && rows_total >= 1024));
+  if (pair) {
+    int64_t pairs = 2 * ((p_dim + PAIR_BM - 1) / PAIR_BM) * ((q_dim + BN - 1) / BN);
+    if (pairs > usable_sms(dev) / 2) pairs = usable_sms(dev) / 2;
+    cudaError_t e = cudaFuncSetAttribute(wgrad_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+    if (e != cudaSuccess) return cuda_status(e);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = PAIR_SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cuda_status(cudaLaunchKernelEx(&cfg, wgrad_pair_kernel, tmP, tmQ, wp));
+  }
   int64_t grid = 2 * ((p_dim + BM - 1) / BM) * ((q_dim + BN - 1) / BN);
   if (grid > usable_sms(dev)) grid = usable_sms(dev);
   cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
@@ -1505,43 +1809,53 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
   const DeviceInfo& dev = device_info();
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
 
-  // scattered masks: routed-order copies of g and a (made only then) replace every row gather below
+  // With scratch for routed-order copies of g and a, every GEMM below reads whole tiles of consecutive
+  // rows: dx is then the down-projection kernel of the FFN (routed A, rows scattered back to token
+  // order) and the weight gradients run on CTA pairs.  The two copies cost 4 * M * (N + K) bytes of
+  // traffic and pay for themselves for every mask (identity routing at M=32768, K=N=4096:
+  // 958 -> 1078 TFLOP/s even with the single-CTA weight-gradient kernel).  Without scratch the
+  // kernels gather token rows themselves.
   const bool copies = g_copy && a_copy;
   const int64_t copy_rows = ffnk_route_capacity(M) + 512;
-  const int thr = copy_threshold((N + K) / 2);   // one decision shared by the dx GEMM and the weight gradients
   if (copies && ((reinterpret_cast<uintptr_t>(g_copy) | reinterpret_cast<uintptr_t>(a_copy)) & 15)) return FFNK_ERR_ALIGN;
   // dx: the forward kernel on g with the weights seen as [N, K] (contraction over N)
   {
     AMaps tmA;
     CUtensorMap tmB[4];
-    int r = gather_maps(tmA, g, N, M, ldg);
-    if (r) return r;
+    int r;
     if (copies) {
-      if ((r = permute_rows_launch(g, ldg, perm, counts, g_copy, N, M, N, thr, stream))) return r;
-      if ((r = permute_rows_launch(a, lda, perm, counts, a_copy, K, M, K, thr, stream))) return r;
-      if ((r = make_tensor_map_2d(&tmA.m[COPY_MAP], g_copy, N, copy_rows, N, BK, BM))) return r;
+      if ((r = permute_rows_launch(g, ldg, perm, counts, g_copy, N, M, N, 0, stream))) return r;
+      if ((r = permute_rows_launch(a, lda, perm, counts, a_copy, K, M, K, 0, stream))) return r;
+      if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], g_copy, N, copy_rows, N, BK, BM))) return r;
+      for (int i = 0; i <= COPY_MAP; ++i)
+        if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
+    } else if ((r = gather_maps(tmA, g, N, M, ldg))) {
+      return r;
     }
     bool mn1 = false, mn2 = false;
-    const TileChoice tile = pick_tile(M, K, A_GATHER, EPI_STORE, weights_k_major(b_stride_n, b_stride_k, N));
+    const TileChoice tile = pick_tile(M, K, copies ? A_ROUTED : A_GATHER, EPI_STORE,
+                                      weights_k_major(b_stride_n, b_stride_k, N));
     if ((r = weight_map(&tmB[0], WeightView{b1, b_stride_n, b_stride_k, N, K}, &mn1, tile.bn / 2))) return r;
     if ((r = weight_map(&tmB[2], WeightView{b2, b_stride_n, b_stride_k, N, K}, &mn2, tile.bn / 2))) return r;
     tmB[1] = tmB[0];
     tmB[3] = tmB[2];
     GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(da), ldda, static_cast<int>(K), static_cast<int>(N),
                  static_cast<int>(M), pick_group_m(N), max_run_rows(), status, g_prof_buffer};
-    p.a_copy = copies ? thr : 0;
-    r = launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, s);
+    r = copies ? launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, s)
+               : launch_gemm<A_GATHER, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, s);
     if (r) return r;
   }
   // dW: output in the weight's storage order; P supplies the storage rows, Q the storage columns
   {
-    const void* P = k_major ? g : a;
-    const void* Q = k_major ? a : g;
-    const int64_t ldp = k_major ? ldg : lda, ldq = k_major ? lda : ldg;
+    const void* gg = copies ? g_copy : g;
+    const void* aa = copies ? a_copy : a;
+    const int64_t lg = copies ? N : ldg, la = copies ? K : lda;
+    const void* P = k_major ? gg : aa;
+    const void* Q = k_major ? aa : gg;
+    const int64_t ldp = k_major ? lg : la, ldq = k_major ? la : lg;
     const int64_t p_dim = k_major ? N : K, q_dim = k_major ? K : N;
-    return launch_wgrad(P, ldp, p_dim, Q, ldq, q_dim, M, db1, db2, k_major ? b_stride_n : b_stride_k, 0, perm, counts,
-                        status, s, copies ? (k_major ? g_copy : a_copy) : nullptr,
-                        copies ? (k_major ? a_copy : g_copy) : nullptr, copy_rows, thr);
+    return launch_wgrad(P, ldp, p_dim, Q, ldq, q_dim, copies ? copy_rows : M, db1, db2,
+                        k_major ? b_stride_n : b_stride_k, copies ? 1 : 0, perm, counts, status, s);
   }
 }
 

@@ -64,6 +64,29 @@ def main():
     L = lib()
     st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
 
+    if a.what == "waits" and a.bwd:
+        # weight-gradient kernel of the MaskedLinear backward: who waits for whom
+        M, K, N = a.M, a.K, a.N
+        c = linear_case(M, K, N, seed=0, mask=edge_mask(M, a.mask, 0)).to(dev)
+        g = torch.randn((M, N), device=dev, dtype=torch.bfloat16)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        prof = torch.zeros(sms * 8, dtype=torch.int64, device=dev)
+        for _ in range(a.warmup):
+            _bf16_linear_backward(g, c.x, c.wv.T, c.wt.T, c.mask)
+        torch.cuda.synchronize()
+        L.ffnk_debug_profile_buffer(prof.data_ptr())
+        ms = timeit(lambda: _bf16_linear_backward(g, c.x, c.wv.T, c.wt.T, c.mask), 1, 0)
+        L.ffnk_debug_profile_buffer(None)
+        p = prof.view(sms, 8).cpu().double()
+        tot = float(p[:, 0].mean())
+        emit(kernel="wgrad (inside linear_bwd)", M=M, K=K, N=N, mask=a.mask, bwd_ms=ms, mma_cycles=tot,
+             mma_wait_operands_pct=100 * float(p[:, 1].mean()) / tot,
+             mma_wait_accumulator_pct=100 * float(p[:, 2].mean()) / tot,
+             producer_wait_stage_pct=100 * float(p[:, 3].mean() / p[:, 4].mean()),
+             tiles_per_cta=float(p[:, 7].mean()), mma_cycles_min=float(p[:, 0].min()), mma_cycles_max=float(p[:, 0].max()))
+        check_status()
+        return
+
     if a.what == "waits":
         M, d, h = a.M, a.d, a.h
         c = ffn_case(M, d, h, seed=0, mask=edge_mask(M, a.mask, 0)).to(dev)
