@@ -883,10 +883,6 @@ struct WgradParams {
   int max_run_rows;
   int* status;
   int routed = 0;   // 1: P and Q are in routed order (row = group base + list position), no index list
-  int copies = 0;   // > 0: routed-order copies of P and Q exist (second pair of maps) and are read instead
-                    //    whenever the mask's average run is shorter than this (decided on the device);
-                    //    their height is copy_rows
-  int copy_rows = 0;
   long long* prof = nullptr;   // optional per-CTA wait-cycle counters (8 per CTA), as in GemmParams
 };
 
@@ -917,8 +913,7 @@ __device__ __forceinline__ WgradTile decode_wgrad_tile(int t, int p_tiles, int q
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS_MAX, 1)
-wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm, const __grid_constant__ WMaps pmc,
-             const __grid_constant__ WMaps qmc, const WgradParams p) {
+wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm, const WgradParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -945,8 +940,6 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
     for (int i = 0; i < RUN_LEVELS; ++i) {
       tma_prefetch_desc(&pm.m[i]);
       tma_prefetch_desc(&qm.m[i]);
-      tma_prefetch_desc(&pmc.m[i]);
-      tma_prefetch_desc(&qmc.m[i]);
     }
   }
   if (warp == 1) {
@@ -969,11 +962,10 @@ wgrad_kernel(const __grid_constant__ WMaps pm, const __grid_constant__ WMaps qm,
     uint32_t phase = 0;
     int issued = 0;
     bool ok = true;
-    const bool use_copies = p.copies && mask_is_scattered(p.counts, p.copies);
-    const bool routed = p.routed || use_copies;
-    const WMaps* mp = use_copies ? &pmc : &pm;
-    const WMaps* mq = use_copies ? &qmc : &qm;
-    const int pad_row = use_copies ? p.copy_rows : p.pad_row;
+    const bool routed = p.routed != 0;
+    const WMaps* mp = &pm;
+    const WMaps* mq = &qm;
+    const int pad_row = p.pad_row;
     const int gi = lane & 15;     // which group of four list rows inside the k-step
     const int half = lane >> 4;   // which 64-column block (of a pair)
     long long t_begin = clock64(), t_wait = 0;
@@ -1596,25 +1588,15 @@ static int wgrad_maps(WMaps& w, const void* base, int64_t cols, int64_t rows, in
 
 static int launch_wgrad(const void* P, int64_t ldp, int64_t p_dim, const void* Q, int64_t ldq, int64_t q_dim,
                         int64_t rows_total, void* out_v, void* out_t, int64_t ldo, int routed, const int32_t* perm,
-                        const int32_t* counts, int32_t* status, cudaStream_t s, const void* P_copy = nullptr,
-                        const void* Q_copy = nullptr, int64_t copy_rows = 0, int copy_thr = 0) {
+                        const int32_t* counts, int32_t* status, cudaStream_t s) {
   const DeviceInfo& dev = device_info();
-  WMaps tmP, tmQ, tmPc, tmQc;
+  WMaps tmP, tmQ;
   int r = wgrad_maps(tmP, P, p_dim, rows_total, ldp);
   if (r) return r;
   if ((r = wgrad_maps(tmQ, Q, q_dim, rows_total, ldq))) return r;
-  const bool copies = P_copy && Q_copy;
-  if (copies) {
-    if ((r = wgrad_maps(tmPc, P_copy, p_dim, copy_rows, p_dim))) return r;
-    if ((r = wgrad_maps(tmQc, Q_copy, q_dim, copy_rows, q_dim))) return r;
-  } else {
-    tmPc = tmP;
-    tmQc = tmQ;
-  }
   WgradParams wp{perm, counts, static_cast<__nv_bfloat16*>(out_v), static_cast<__nv_bfloat16*>(out_t), ldo,
                  static_cast<int>(p_dim), static_cast<int>(q_dim), static_cast<int>(rows_total),
-                 max_run_rows() < 64 ? max_run_rows() : 64, status, routed, copies ? copy_thr : 0,
-                 static_cast<int>(copy_rows)};
+                 max_run_rows() < 64 ? max_run_rows() : 64, status, routed};
   wp.prof = g_prof_buffer;
   // operands in routed order and an output big enough for 256 x 256 tiles: the CTA-pair kernel
   // (FFNK_WGRAD_PAIR=0/1 overrides for experiments)
@@ -1644,7 +1626,7 @@ static int launch_wgrad(const void* P, int64_t ldp, int64_t p_dim, const void* Q
   if (grid > usable_sms(dev)) grid = usable_sms(dev);
   cudaError_t e = cudaFuncSetAttribute(wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
   if (e != cudaSuccess) return cuda_status(e);
-  wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, tmPc, tmQc, wp);
+  wgrad_kernel<<<static_cast<unsigned>(grid), GEMM_THREADS, GEMM_SMEM, s>>>(tmP, tmQ, wp);
   return cuda_status(cudaGetLastError());
 }
 

@@ -78,9 +78,9 @@ def _mask_route(mask, M, device, rt: Route | None) -> Route:
 def _copy_scratch(M: int, width: int, dev):
     """Scratch for a routed-order copy of an [M, width] activation, or None for small M.
 
-    The library fills and reads it only when the routing statistics say the mask is scattered
+    The forward fills and reads it only when the routing statistics say the mask is scattered
     (runs of same-modality tokens averaging under max(32, columns / 6) rows); masks made of long
-    spans never touch it.
+    spans never touch it.  The backward always works from routed-order copies when it gets them.
     FFNK_LINEAR_COPY=0 withholds it (the GEMM then always gathers token rows itself)."""
     if os.environ.get("FFNK_LINEAR_COPY", "1") == "0" or M < 512:
         return None

@@ -105,8 +105,11 @@ int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const void* b2, 
  *     db1 = a[mask]^T @ g[mask],   db2 = a[~mask]^T @ g[~mask]
  * db1/db2 are written with the same strides as b1/b2 (the reference allocates them with
  * empty_like, ffn_kernel/linear.py:475).
- * g_copy [(cap + 512), N], a_copy [(cap + 512), K]: optional scratch (both or neither), used as
- * in ffnk_linear_fwd when the mask is scattered.
+ * g_copy [(cap + 512), N], a_copy [(cap + 512), K]: optional scratch (both or neither).  With it
+ * the call first copies g and a into routed order (for every mask) and all three GEMMs read whole
+ * tiles of consecutive rows: dx with the kernel of ffnk_ffn_down, the weight gradients on CTA
+ * pairs (M=32768, K=N=4096: 1.82 ms against 2.12-2.29 ms without).  Without it the kernels
+ * gather token rows themselves; worthwhile only for small M.
  * ------------------------------------------------------------------------------------- */
 int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
                     int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm, const int32_t* counts, void* da,
