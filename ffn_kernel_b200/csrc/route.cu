@@ -33,6 +33,87 @@ constexpr uint32_t kFlagAgg = 1u << 30;
 constexpr uint32_t kFlagInc = 2u << 30;
 constexpr uint32_t kValMask = (1u << 30) - 1;
 
+// The 32 mask bytes of one thread as a bit mask (bit i = token base + i is visual), how many of
+// the 32 tokens exist, and how many runs start among them (a token whose modality differs from its
+// predecessor's; token 0 always).
+struct ThreadTokens {
+  uint32_t bits;
+  int valid;
+  int nruns;
+};
+
+__device__ __forceinline__ ThreadTokens load_thread_tokens(const uint8_t* __restrict__ mask, int M, int base) {
+  uint32_t w[kRoutePerThread / 4] = {};
+  int valid = M - base;
+  valid = valid < 0 ? 0 : (valid > kRoutePerThread ? kRoutePerThread : valid);
+  if (valid == kRoutePerThread && ((reinterpret_cast<uintptr_t>(mask) & 15) == 0)) {
+    const uint4 v0 = *reinterpret_cast<const uint4*>(mask + base);
+    const uint4 v1 = *reinterpret_cast<const uint4*>(mask + base + 16);
+    w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w;
+    w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
+  } else {
+    for (int i = 0; i < valid; ++i) w[i >> 2] |= static_cast<uint32_t>(mask[base + i]) << (8 * (i & 3));
+  }
+  ThreadTokens t;
+  t.bits = 0;
+#pragma unroll
+  for (int i = 0; i < kRoutePerThread; ++i) t.bits |= (((w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0 ? 1u : 0u) << i;
+  t.valid = valid;
+  t.nruns = 0;
+  if (valid > 0) {
+    const uint32_t prev = base > 0 ? (mask[base - 1] != 0 ? 1u : 0u) : ((t.bits & 1u) ^ 1u);
+    const uint32_t vmask = valid == 32 ? 0xFFFFFFFFu : ((1u << valid) - 1u);
+    t.nruns = __popc((t.bits ^ ((t.bits << 1) | prev)) & vmask);
+  }
+  return t;
+}
+
+// Block-wide scan of the per-thread visual counts.  Returns the number of visual tokens before
+// this thread inside the tile; *tile_v = visual tokens of the tile.  Contains one __syncthreads().
+__device__ __forceinline__ int block_exclusive_scan(int nv, int* s_warp, int* tile_v) {
+  const int tid = threadIdx.x;
+  int incl = nv;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if ((tid & 31) >= o) incl += n;
+  }
+  if ((tid & 31) == 31) s_warp[tid >> 5] = incl;
+  __syncthreads();
+  int warp_off = 0, total = 0;
+#pragma unroll
+  for (int i = 0; i < kRouteThreads / 32; ++i) {
+    const int c = s_warp[i];
+    if (i < (tid >> 5)) warp_off += c;
+    total += c;
+  }
+  *tile_v = total;
+  return warp_off + incl - nv;
+}
+
+// Compaction inside the tile: visual indices to s_list[0..tile_v), text to s_list[tile_v..tile_len).
+// The warp goes through its 32 threads' token groups one after the other, lane l taking token l of
+// the group: the lanes of one modality then write consecutive words (no bank conflicts; a thread
+// writing its own 32 tokens one by one puts the lanes 16 words apart, a 16-way conflict per store).
+__device__ __forceinline__ void compact_tile(int* s_list, int tile, uint32_t bits, int ev, int valid, int tile_v) {
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const uint32_t below = (1u << lane) - 1u;
+#pragma unroll 4
+  for (int r = 0; r < 32; ++r) {
+    const uint32_t b = __shfl_sync(0xFFFFFFFFu, bits, r);
+    const int ev_r = __shfl_sync(0xFFFFFFFFu, ev, r);
+    const int valid_r = __shfl_sync(0xFFFFFFFFu, valid, r);
+    if (lane < valid_r) {
+      const int tid_r = (tid & ~31) + r;
+      const int tok = tile * kRouteTile + tid_r * kRoutePerThread + lane;
+      const int before = __popc(b & below);
+      if ((b >> lane) & 1u) s_list[ev_r + before] = tok;
+      else s_list[tile_v + (tid_r * kRoutePerThread - ev_r) + (lane - before)] = tok;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __restrict__ mask, int M, int cap,
                                                               int* __restrict__ perm, int* __restrict__ counts,
                                                               uint32_t* __restrict__ ws,  // [0] run total, [1..tiles] tile state, [tiles+1] finished tiles
@@ -49,54 +130,17 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
   volatile uint32_t* state = ws + 1;
 
   const int base = tile * kRouteTile + tid * kRoutePerThread;
-  // 32 mask bytes of this thread
-  uint32_t w[kRoutePerThread / 4] = {};
-  int valid = M - base;
-  valid = valid < 0 ? 0 : (valid > kRoutePerThread ? kRoutePerThread : valid);
-  if (valid == kRoutePerThread && ((reinterpret_cast<uintptr_t>(mask) & 15) == 0)) {
-    const uint4 v0 = *reinterpret_cast<const uint4*>(mask + base);
-    const uint4 v1 = *reinterpret_cast<const uint4*>(mask + base + 16);
-    w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w;
-    w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
-  } else {
-    for (int i = 0; i < valid; ++i) w[i >> 2] |= static_cast<uint32_t>(mask[base + i]) << (8 * (i & 3));
-  }
-  // bit i of `bits` = token base+i is visual
-  uint32_t bits = 0;
-#pragma unroll
-  for (int i = 0; i < kRoutePerThread; ++i) bits |= (((w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0 ? 1u : 0u) << i;
+  const ThreadTokens tt = load_thread_tokens(mask, M, base);
+  const uint32_t bits = tt.bits;
+  const int valid = tt.valid;
   const int nv = __popc(bits);
-  // run starts among this thread's tokens: a token whose modality differs from its predecessor's
-  // (token 0 always).  The consumers use the total to tell span-structured masks from scattered ones.
-  int nruns = 0;
-  if (valid > 0) {
-    const uint32_t prev = base > 0 ? (mask[base - 1] != 0 ? 1u : 0u) : ((bits & 1u) ^ 1u);
-    const uint32_t vmask = valid == 32 ? 0xFFFFFFFFu : ((1u << valid) - 1u);
-    nruns = __popc((bits ^ ((bits << 1) | prev)) & vmask);
-  }
   if (tid == 0) s_runs = 0;
-
-  // block-wide exclusive scan of nv
-  int incl = nv;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-    if ((tid & 31) >= o) incl += n;
-  }
-  if ((tid & 31) == 31) s_warp[tid >> 5] = incl;
-  __syncthreads();
+  int tile_v = 0;
+  const int ev = block_exclusive_scan(nv, s_warp, &tile_v);   // visual tokens before this thread, in tile
   {
-    const int wr = __reduce_add_sync(0xFFFFFFFFu, nruns);
+    const int wr = __reduce_add_sync(0xFFFFFFFFu, tt.nruns);
     if ((tid & 31) == 0 && wr) atomicAdd(&s_runs, wr);
   }
-  int warp_off = 0, tile_v = 0;
-#pragma unroll
-  for (int i = 0; i < kRouteThreads / 32; ++i) {
-    const int c = s_warp[i];
-    if (i < (tid >> 5)) warp_off += c;
-    tile_v += c;
-  }
-  const int ev = warp_off + incl - nv;                 // visual tokens before this thread, in tile
   const int tile_len = min(kRouteTile, M - tile * kRouteTile);
   const int tile_t = tile_len - tile_v;
 
@@ -162,17 +206,7 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
     }
   }
 
-  // compact inside the tile: visual indices to s_list[0..tile_v), text to s_list[tile_v..tile_len)
-  {
-    int pv = ev, pt = tile_v + (tid * kRoutePerThread - ev);
-#pragma unroll
-    for (int i = 0; i < kRoutePerThread; ++i) {
-      if (i < valid) {
-        if ((bits >> i) & 1u) s_list[pv++] = base + i;
-        else s_list[pt++] = base + i;
-      }
-    }
-  }
+  compact_tile(s_list, tile, bits, ev, valid, tile_v);
   __syncthreads();
   if (!s_ok) return;
   const int pre_v = s_excl;
@@ -198,8 +232,107 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
   }
 }
 
+// -------------------------------------------------------------------------------------------
+// Long masks (more than kLookBackMaxTiles tiles): two kernels and no waiting.  With thousands of
+// tiles in flight the look-back of route_kernel turns into every tile polling the same few cache
+// lines of tile states, and the chain of prefixes, not DRAM, sets the pace (M = 2^26: 1.3 TB/s of
+// the 5 bytes per token).  Here the first kernel counts (1 byte per token read) and its last block
+// to finish turns the per-tile counts into exclusive prefixes; the second kernel reads the mask
+// again and writes the lists (6 bytes per token in all).
+// ws: [0] run total, [1..tiles] per-tile visual count -> exclusive prefix, [tiles+1] finished tiles.
+// -------------------------------------------------------------------------------------------
+constexpr int kLookBackMaxTiles = 128;
+
+__global__ void __launch_bounds__(kRouteThreads) route_count_kernel(const uint8_t* __restrict__ mask, int M, int cap,
+                                                                    int* __restrict__ counts,
+                                                                    uint32_t* __restrict__ ws) {
+  __shared__ int s_warp[kRouteThreads / 32];
+  __shared__ int s_runs, s_last;
+  const int tid = threadIdx.x;
+  const int tile = blockIdx.x;
+  const int num_tiles = gridDim.x;
+  const ThreadTokens tt = load_thread_tokens(mask, M, tile * kRouteTile + tid * kRoutePerThread);
+  if (tid == 0) s_runs = 0;
+  int tile_v = 0;
+  block_exclusive_scan(__popc(tt.bits), s_warp, &tile_v);
+  {
+    const int wr = __reduce_add_sync(0xFFFFFFFFu, tt.nruns);
+    if ((tid & 31) == 0 && wr) atomicAdd(&s_runs, wr);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    ws[1 + tile] = static_cast<uint32_t>(tile_v);
+    atomicAdd(&ws[0], static_cast<uint32_t>(s_runs));
+    __threadfence();
+    s_last = atomicAdd(&ws[1 + num_tiles], 1u) == static_cast<uint32_t>(num_tiles - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // every other block has published its count: exclusive prefix over the tiles, in place
+  __threadfence();
+  volatile uint32_t* cnt = ws + 1;
+  const int per = (num_tiles + kRouteThreads - 1) / kRouteThreads;
+  const int lo = min(num_tiles, tid * per), hi = min(num_tiles, lo + per);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += static_cast<int>(cnt[i]);
+  int total = 0;
+  int run = block_exclusive_scan(sum, s_warp, &total);
+  for (int i = lo; i < hi; ++i) {
+    const int c = static_cast<int>(cnt[i]);
+    cnt[i] = static_cast<uint32_t>(run);
+    run += c;
+  }
+  if (tid == 0) {
+    counts[0] = total;
+    counts[1] = M - total;
+    counts[2] = cap;
+    counts[3] = M;
+    counts[4] = static_cast<int>(atomicAdd(&ws[0], 0u));
+  }
+}
+
+__global__ void __launch_bounds__(kRouteThreads) route_scatter_kernel(const uint8_t* __restrict__ mask, int M, int cap,
+                                                                      int* __restrict__ perm,
+                                                                      const uint32_t* __restrict__ ws) {
+  __shared__ int s_list[kRouteTile];
+  __shared__ int s_warp[kRouteThreads / 32];
+  const int tid = threadIdx.x;
+  const int tile = blockIdx.x;
+  const ThreadTokens tt = load_thread_tokens(mask, M, tile * kRouteTile + tid * kRoutePerThread);
+  int tile_v = 0;
+  const int ev = block_exclusive_scan(__popc(tt.bits), s_warp, &tile_v);
+  const int tile_len = min(kRouteTile, M - tile * kRouteTile);
+  const int tile_t = tile_len - tile_v;
+  compact_tile(s_list, tile, tt.bits, ev, tt.valid, tile_v);
+  __syncthreads();
+  const int pre_v = static_cast<int>(ws[1 + tile]);
+  const int pre_t = tile * kRouteTile - pre_v;
+  for (int i = tid; i < tile_v; i += kRouteThreads) perm[pre_v + i] = s_list[i];
+  for (int i = tid; i < tile_t; i += kRouteThreads) perm[cap + pre_t + i] = s_list[tile_v + i];
+}
+
 __global__ void route_empty_kernel(int* counts, int cap) {
   counts[0] = 0; counts[1] = 0; counts[2] = cap; counts[3] = 0; counts[4] = 0;
+}
+
+// One tile: a single kernel that never looks back (its state word need not be cleared).  Up to
+// kLookBackMaxTiles tiles: the single-pass chained scan.  Beyond: count, then scatter.
+static int route_launch(const uint8_t* mask, int M, int cap, int* perm, int* counts, uint32_t* ws, int* status,
+                        cudaStream_t stream) {
+  const int tiles = (M + kRouteTile - 1) / kRouteTile;
+  if (tiles > 1) {
+    cudaError_t e = cudaMemsetAsync(ws, 0, (static_cast<size_t>(tiles) + 2) * sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return cuda_status(e);
+  }
+  if (tiles <= kLookBackMaxTiles) {
+    route_kernel<<<tiles, kRouteThreads, 0, stream>>>(mask, M, cap, perm, counts, ws, status);
+    return cuda_status(cudaGetLastError());
+  }
+  route_count_kernel<<<tiles, kRouteThreads, 0, stream>>>(mask, M, cap, counts, ws);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_status(e);
+  route_scatter_kernel<<<tiles, kRouteThreads, 0, stream>>>(mask, M, cap, perm, ws);
+  return cuda_status(cudaGetLastError());
 }
 
 }  // namespace ffnk
@@ -225,15 +358,8 @@ extern "C" int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* c
   }
   if (!mask || !perm || !workspace) return FFNK_ERR_NULL;
   if (reinterpret_cast<uintptr_t>(perm) & 15) return FFNK_ERR_ALIGN;
-  const int tiles = static_cast<int>((M + kRouteTile - 1) / kRouteTile);
-  // a single tile never looks back, so its state word need not be cleared
-  if (tiles > 1) {
-    cudaError_t e = cudaMemsetAsync(workspace, 0, ffnk_route_workspace_bytes(M), stream);
-    if (e != cudaSuccess) return cuda_status(e);
-  }
-  route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,
-                                                    counts, static_cast<uint32_t*>(workspace), status);
-  return cuda_status(cudaGetLastError());
+  return route_launch(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm, counts,
+                      static_cast<uint32_t*>(workspace), status, stream);
 }
 
 // -------------------------------------------------------------------------------------------
@@ -426,13 +552,7 @@ extern "C" int ffnk_route_noalloc(const void* mask, int64_t M, int32_t* perm, in
   uint32_t* scratch = nullptr;
   const int r = route_scratch_address(&scratch);
   if (r) return r;
-  const int tiles = static_cast<int>((M + kRouteTile - 1) / kRouteTile);
-  // the array still holds the previous call's tile states: clear the part this call uses
-  if (tiles > 1) {
-    cudaError_t e = cudaMemsetAsync(scratch, 0, (static_cast<size_t>(tiles) + 2) * sizeof(uint32_t), stream);
-    if (e != cudaSuccess) return cuda_status(e);
-  }
-  route_kernel<<<tiles, kRouteThreads, 0, stream>>>(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm,
-                                                    counts, scratch, status);
-  return cuda_status(cudaGetLastError());
+  // the array still holds the previous call's tile states: route_launch clears the part this call uses
+  return route_launch(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm, counts, scratch, status,
+                      stream);
 }

@@ -23,7 +23,8 @@ def _check(mask_cpu, dev):
     assert rt.counts.tolist()[:5] == [len(ov), len(ot), rt.cap, mask_cpu.numel(), runs]
 
 
-@pytest.mark.parametrize("M", [1, 2, 15, 16, 17, 127, 128, 129, 1000, 4095, 4096, 4097, 4099, 8192, 65537, 1 << 20])
+@pytest.mark.parametrize("M", [1, 2, 15, 16, 17, 127, 128, 129, 1000, 4095, 4096, 4097, 4099, 8192, 65537, 1 << 20,
+                               (1 << 20) + 1, 3000001])   # the last two: more than 128 tiles, the two-kernel path
 @pytest.mark.parametrize("kind", ["bernoulli", "all_visual", "all_text", "alternating", "span"])
 def test_route_bit_exact(dev, M, kind):
     _check(edge_mask(M, kind, seed=M), dev)
