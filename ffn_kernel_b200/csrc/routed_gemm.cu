@@ -498,21 +498,26 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      long long t_begin = clock64(), t_full = 0, t_tmem = 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        long long tw = clock64();
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
           report(p.status, ST_TIMEOUT_MMA_TMEM);
           break;
         }
+        t_tmem += clock64() - tw;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN_T;
         for (int ks = 0; ks < k_steps; ++ks) {
+          tw = clock64();
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             report(p.status, ST_TIMEOUT_MMA_FULL);
             ok = false;
             break;
           }
+          t_full += clock64() - tw;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * TSTAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
@@ -527,6 +532,12 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
           if (++stage == TSTAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tfull[acc]);
+      }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = clock64() - t_begin;
+        p.prof[blockIdx.x * 8 + 1] = t_full;
+        p.prof[blockIdx.x * 8 + 2] = t_tmem;
+        p.prof[blockIdx.x * 8 + 7] = it;
       }
     }
     __syncwarp();

@@ -95,10 +95,15 @@ def main():
         y = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         prof = torch.zeros(sms * 8, dtype=torch.int64, device=dev)
+        xr = torch.empty((rt.cap + 512, d), device=dev, dtype=torch.bfloat16)
+        L.ffnk_permute_rows(c.x.data_ptr(), d, rt.perm.data_ptr(), rt.counts.data_ptr(), xr.data_ptr(), d, M, d, sp)
         launches = {
             "ffn_gateup(gather in kernel)": lambda: L.ffnk_ffn_gateup(
                 c.x.data_ptr(), d, c.w1.data_ptr(), c.w3.data_ptr(), c.u1.data_ptr(), c.u3.data_ptr(), 1, d,
                 rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), h, 0, 1, M, d, h, st, sp),
+            "ffn_gateup(routed input)": lambda: L.ffnk_ffn_gateup(
+                xr.data_ptr(), d, c.w1.data_ptr(), c.w3.data_ptr(), c.u1.data_ptr(), c.u3.data_ptr(), 1, d,
+                rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(), h, 1, 1, M, d, h, st, sp),
             "ffn_down": lambda: L.ffnk_ffn_down(
                 inter.data_ptr(), h, c.w2.data_ptr(), c.u2.data_ptr(), 1, h, rt.perm.data_ptr(), rt.counts.data_ptr(),
                 y.data_ptr(), d, M, d, h, st, sp),
@@ -112,10 +117,14 @@ def main():
             ms = timeit(fn, 1, 0)
             L.ffnk_debug_profile_buffer(None)
             p = prof.view(sms, 8).cpu().double()
-            lead = p[0::2]
-            if float(lead[:, 0].sum()) == 0:
-                emit(kernel=name, note="no counters: this launch did not use the CTA-pair kernel (set FFNK_PAIR=1)")
+            if float(p[1::2, 0].sum()) > 0:
+                # single-CTA kernel: every CTA issues MMAs; only the MMA issuer keeps counters
+                tot = float(p[:, 0].mean())
+                emit(kernel=name + " [single CTA]", M=M, d=d, h=h, mask=a.mask, ms=ms, mma_cycles=tot,
+                     sm_mhz=tot / ms / 1e3, mma_wait_operands_pct=100 * float(p[:, 1].mean()) / tot,
+                     mma_wait_accumulator_pct=100 * float(p[:, 2].mean()) / tot, tiles_per_cta=float(p[:, 7].mean()))
                 continue
+            lead = p[0::2]
             tot = float(lead[:, 0].mean())
             emit(kernel=name, M=M, d=d, h=h, mask=a.mask, ms=ms, mma_cycles=tot, sm_mhz=tot / ms / 1e3,
                  mma_wait_operands_pct=100 * float(lead[:, 1].mean()) / tot,
