@@ -56,6 +56,15 @@ def test_emulated_ranks_match_oracle(dev, world, M, d, h, kind):
     assert O.max_rel_err(y, ref) < TOL
 
 
+def test_wide_single_cta_tiles(dev):
+    # enough 256-column tiles to fill the SMs but fewer than 4096 rows: the single-CTA 128 x 256 kernel
+    M, d, h, world = 2000, 2560, 384, 2
+    c = ffn_case(M, d, h, seed=11, mask=edge_mask(M, "span", seed=3))
+    ref = O.masked_ffn(*c.apply_args())
+    y, _, _ = _emulated_tp_forward(c.to(dev), world, dev)
+    assert O.max_rel_err(y, ref) < TOL
+
+
 def test_every_owned_row_is_written_exactly_where_expected(dev):
     # after one pass, the NaN fill survives only in rows no token maps to (beyond M)
     M, d, h, world = 1001, 136, 320, 4
