@@ -58,21 +58,63 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the clock-event (throttle) reasons while the timed region runs.
+
+    Read-only NVML queries from a thread of this process every few milliseconds (a timed region
+    of 20 steps lasts well under 100 ms, less than nvidia-smi needs to print its first line);
+    `nvidia-smi -lms` in a child process is the fallback when the NVML binding is missing."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                   0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
         self.proc = None
         self.lines = []
+        self.samples = []          # (sm_mhz, reason bit mask, watts)
+        self.nvml = None
+        self.running = False
+        self.source = None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+
+    def _poll(self):
+        nv, h = self.nvml
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while self.running:
+            try:
+                self.samples.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), int(reasons_fn(h)),
+                                     nv.nvmlDeviceGetPowerUsage(h) / 1000.0))
+            except Exception:
+                pass
+            time.sleep(0.003)
 
     def start(self):
+        try:
+            self.nvml = self._nvml_handle()
+            self.max_mhz = float(self.nvml[0].nvmlDeviceGetMaxClockInfo(self.nvml[1], self.nvml[0].NVML_CLOCK_SM))
+            self.running = True
+            self.source = "nvml"
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.source = "nvidia-smi"
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except Exception:
@@ -83,6 +125,18 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.running = False
+            self.thread.join(timeout=2)
+            if not self.samples:
+                return dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=["no samples"], source="nvml")
+            sm = [v[0] for v in self.samples]
+            mask = 0
+            for v in self.samples:
+                mask |= v[1]
+            reasons = sorted(name for bit, name in self.REASON_BITS.items() if mask & bit)
+            return dict(sm_mhz=statistics.median(sm), sm_min_mhz=min(sm), sm_max_mhz=self.max_mhz, reasons=reasons,
+                        samples=len(sm), watts=statistics.median(v[2] for v in self.samples), source="nvml")
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         self.proc.terminate()
@@ -107,7 +161,8 @@ class ClockSampler:
         if not sm:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
         busy = [v for v in sm if v > 0.5 * max(sm)] or sm
-        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm),
+                    source="nvidia-smi")
 
 
 # ------------------------------------------------------------------------------------------------
@@ -213,10 +268,12 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+        if sampler.source != "nvml":
+            time.sleep(0.3)
     barrier()
     ffn_mod.PHASE_HOOK = hook
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.samples.clear()            # keep only what is sampled while the timed steps run
     e0.record()
     for _ in range(args.steps):
         step()
@@ -231,6 +288,36 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / args.steps
+
+    # The SM clock the kernels actually ran at: cycles counted by the MMA-issuing threads of the
+    # down-projection kernel (clock64) over that launch's duration (CUDA events).  NVML reports the
+    # granted clock, which stays near the maximum while the power cap gates the tensor pipes.
+    if rank == 0 and clocks is not None and mode != "tp":
+        try:
+            from ffn_kernel_b200._lib import lib as _lib
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            prof = torch.zeros(sms * 8, dtype=torch.int64, device=dev)
+            probe = []
+            ffn_mod.PHASE_HOOK = lambda name: (probe.append((name, torch.cuda.Event(enable_timing=True))),
+                                               probe[-1][1].record())
+            _lib().ffnk_debug_profile_buffer(prof.data_ptr())
+            for _ in range(3):
+                probe.clear()
+                step()
+            _lib().ffnk_debug_profile_buffer(None)
+            ffn_mod.PHASE_HOOK = None
+            torch.cuda.synchronize()
+            ev = dict(probe)
+            down_probe_ms = ev["down"].elapsed_time(ev["end"])
+            cyc = prof.view(sms, 8)[0::2, 0].double()
+            cyc = cyc[cyc > 0]
+            if cyc.numel() and down_probe_ms > 0:
+                clocks["sm_mhz_in_kernel"] = float(cyc.mean()) / down_probe_ms / 1e3
+        except Exception as exc:
+            clocks["sm_mhz_in_kernel"] = None
+            clocks["in_kernel_note"] = f"{type(exc).__name__}: {exc}"[:120]
+        finally:
+            ffn_mod.PHASE_HOOK = None
 
     # gate/up launch durations from the events recorded on the launching stream
     names = [n for n, _ in phase_events]

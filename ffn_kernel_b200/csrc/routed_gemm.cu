@@ -69,6 +69,7 @@ __host__ __device__ constexpr bool epi_glu(int e) { return e == EPI_SWIGLU || e 
 enum { OUT_SCATTER = 0, OUT_ROUTED = 1, OUT_PEER = 2 };
 constexpr int MAX_PEERS = 8;
 constexpr int PEER_STAGING = 8 * 4096;   // one 32-row x 128-byte transposition buffer per epilogue warp
+constexpr int GLU_STAGING = 8 * 2048;    // one 32-row x 64-byte transposition buffer per epilogue warp
 
 struct GemmParams {
   const int* perm;      // routing lists
@@ -272,12 +273,10 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, const GemmParams& p
               t3[e] = __uint_as_float(u[j * 8 + e]);
             }
             if constexpr (EPI == EPI_SWIGLU_SAVE) {
-              // the backward pass differentiates the bf16 values it is handed, so H is formed from those
-              const uint4 p1 = pack_bf16x8(t1), p3 = pack_bf16x8(t3);
-              *reinterpret_cast<uint4*>(p.aux0 + off) = p1;
-              *reinterpret_cast<uint4*>(p.aux1 + off) = p3;
-              unpack_bf16x8(p1, t1);
-              unpack_bf16x8(p3, t3);
+              // H below is formed from the fp32 accumulators, exactly as in the inference epilogue (the
+              // training and inference forward give the same y); only the saved copies are rounded
+              *reinterpret_cast<uint4*>(p.aux0 + off) = pack_bf16x8(t1);
+              *reinterpret_cast<uint4*>(p.aux1 + off) = pack_bf16x8(t3);
             }
 #pragma unroll
             for (int e = 0; e < 8; ++e) h[e] = silu_mul(t1[e], t3[e]);
@@ -286,6 +285,64 @@ __device__ __forceinline__ void epilogue_row(uint32_t taddr, const GemmParams& p
         }
       }
     }
+  }
+}
+
+// SwiGLU epilogue of one warp's 32 accumulator rows with coalesced stores.  A lane owns one row of
+// the accumulator, so storing straight from registers puts 16 bytes into 32 different rows per
+// instruction: 32 cache lines per store, and with three outputs per element (H, T1, T3 in the
+// training forward) the load/store unit, not the tensor pipe, sets the pace of short-K tiles.
+// Each 32-column chunk therefore goes through a 2 KiB shared-memory transposition (XOR-swizzled
+// 16-byte pieces, conflict free both ways) and leaves as 64 contiguous bytes per row, eight rows
+// per instruction.  `row_off` = element offset of this lane's destination row, or -1 for no row.
+template <int EPI, int BN_T>
+__device__ __forceinline__ void epilogue_glu_staged(uint32_t taddr, const GemmParams& p, long long row_off, int n_base,
+                                                    int part, int parts, uint8_t* stg, int lane) {
+  constexpr int CH = BN_T / 64;
+  const int pc = lane & 3;
+  long long ro[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) ro[i] = __shfl_sync(0xFFFFFFFFu, row_off, i * 8 + (lane >> 2));
+  uint8_t* wr = stg + lane * 64;
+  const int wsw = (lane >> 1) & 3;
+  auto flush = [&](const float (&v)[32], __nv_bfloat16* base, int n0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] = v[j * 8 + e];
+      *reinterpret_cast<uint4*>(wr + ((j ^ wsw) << 4)) = pack_bf16x8(a);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i * 8 + (lane >> 2);
+      const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4));
+      if (ro[i] >= 0 && n0 + pc * 8 < p.n_out) *reinterpret_cast<uint4*>(base + ro[i] + n0 + pc * 8) = val;
+    }
+    __syncwarp();
+  };
+#pragma unroll 1
+  for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
+    uint32_t g[32], u[32];
+    tmem_ld_32x32(taddr + c * 32, g);              // gate  (t1)
+    tmem_ld_32x32(taddr + BN_T / 2 + c * 32, u);   // up    (t3)
+    tmem_ld_wait();
+    const int n0 = n_base + c * 32;
+    if (n0 >= p.n_out) continue;                   // warp-uniform
+    float t1[32], t3[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      t1[e] = __uint_as_float(g[e]);
+      t3[e] = __uint_as_float(u[e]);
+    }
+    if constexpr (EPI == EPI_SWIGLU_SAVE) {
+      flush(t1, p.aux0, n0);
+      flush(t3, p.aux1, n0);
+    }
+#pragma unroll
+    for (int e = 0; e < 32; ++e) t1[e] = silu_mul(t1[e], t3[e]);
+    flush(t1, p.out, n0);
   }
 }
 
@@ -571,6 +628,9 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       if constexpr (OUT_MODE == OUT_PEER)
         epilogue_rows_peer<BN_T>(taddr, p, peer_dst, tc.nt * BN_T, part, epilogue_parts(),
                                  smem + TSTAGES * TSTAGE_BYTES + 256 + (warp - 2) * 4096, lane);
+      else if constexpr (epi_glu(EPI))
+        epilogue_glu_staged<EPI, BN_T>(taddr, p, valid ? dst_row * p.ldo : -1ll, tc.nt * (BN_T / 2), part,
+                                       epilogue_parts(), smem + TSTAGES * TSTAGE_BYTES + 256 + (warp - 2) * 2048, lane);
       else
         epilogue_row<EPI, BN_T>(taddr, p, dst_row * p.ldo, valid, tc.nt * (epi_glu(EPI) ? BN_T / 2 : BN_T), part, epilogue_parts());
       tc_fence_before();
@@ -849,6 +909,9 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       if constexpr (OUT_MODE == OUT_PEER)
         epilogue_rows_peer<BN>(taddr, p, peer_dst, tc.nt * N_PER_TILE, part, epilogue_parts(),
                                smem + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * 4096, lane);
+      else if constexpr (epi_glu(EPI))
+        epilogue_glu_staged<EPI, BN>(taddr, p, valid ? dst_row * p.ldo : -1ll, tc.nt * N_PER_TILE, part,
+                                     epilogue_parts(), smem + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * 2048, lane);
       else
         epilogue_row<EPI, BN>(taddr, p, dst_row * p.ldo, valid, tc.nt * N_PER_TILE, part, epilogue_parts());
       tc_fence_before();
@@ -1539,7 +1602,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
   const int n_per_tile = epi_glu(EPI) ? tile.bn / 2 : tile.bn;
   const int64_t n_tiles = (p.n_out + n_per_tile - 1) / n_per_tile;
-  constexpr int extra_smem = OUT_MODE == OUT_PEER ? PEER_STAGING : 0;
+  constexpr int extra_smem = OUT_MODE == OUT_PEER ? PEER_STAGING : (epi_glu(EPI) ? GLU_STAGING : 0);
   if (tile.pair) {
     int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
     if (pairs > usable_sms(dev) / 2) pairs = usable_sms(dev) / 2;

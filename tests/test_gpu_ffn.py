@@ -158,6 +158,18 @@ def test_backward_golden(dev):
         assert O.max_rel_err(leaf.grad, z[f"d{n}_f32"]) < TOL, n
 
 
+@pytest.mark.parametrize("M,d,h", [(300, 128, 328), (4099, 1024, 2816)])
+def test_training_forward_equals_inference_forward(dev, M, d, h):
+    # the forward that keeps the pre-activations forms H from the same fp32 accumulators
+    c = ffn_case(M, d, h, seed=M, mask=edge_mask(M, "span", seed=d)).to(dev)
+    y_inf = MaskedFFN.apply(*c.apply_args())
+    args = list(c.apply_args())
+    args[0] = args[0].clone().requires_grad_(True)
+    y_train = MaskedFFN.apply(*args)
+    check_status()
+    assert y_train.requires_grad and torch.equal(y_train.detach(), y_inf)
+
+
 def test_backward_only_when_asked_for(dev):
     c = ffn_case(64, 64, 64, seed=1).to(dev)
     y = MaskedFFN.apply(*c.apply_args())            # nothing requires grad: inference path

@@ -1,6 +1,7 @@
 """Seeded random shapes, masks and weight layouts: tile tails in every dimension (rows per
 modality around multiples of 128 and 256, K and N that are multiples of 8 but not of 64),
 empty modalities, strided activations.  Every case is checked against the fp32 CPU oracle."""
+import os
 import random
 
 import pytest
@@ -12,6 +13,9 @@ from ffn_kernel_b200.synth import ffn_case, linear_case
 from oracle import masked_ref as O
 
 pytestmark = pytest.mark.gpu
+
+# FFNK_STRESS_SEEDS=N widens the sweep for a one-off soak run
+SEEDS = int(os.environ.get("FFNK_STRESS_SEEDS", "24"))
 
 
 def _random_mask(M, rng):
@@ -35,12 +39,12 @@ def _random_mask(M, rng):
 
 
 def _dims(rng):
-    M = rng.choice([1, 7, 33, 127, 128, 129, 255, 256, 257, 384, 511, 513, 777, 1025, 2049])
+    M = rng.choice([1, 7, 33, 127, 128, 129, 255, 256, 257, 384, 511, 513, 777, 1025, 2049, 4097, 5000])
     pick = lambda: rng.choice([8, 24, 64, 72, 136, 200, 264, 320, 520])
     return M, pick(), pick()
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(SEEDS))
 def test_linear_forward_backward_random(dev, seed):
     rng = random.Random(1000 + seed)
     M, K, N = _dims(rng)
@@ -69,7 +73,7 @@ def test_linear_forward_backward_random(dev, seed):
     assert O.max_rel_err(d1, rd1) < TOL and O.max_rel_err(d2, rd2) < TOL, tag
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(SEEDS))
 def test_ffn_forward_backward_random(dev, seed):
     rng = random.Random(2000 + seed)
     M, d, h = _dims(rng)
