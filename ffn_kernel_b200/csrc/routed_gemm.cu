@@ -210,78 +210,31 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
   return o;
 }
 
-// Epilogue of one accumulator row: this thread owns the TMEM lane at `taddr`, BN_T fp32 columns.
-// `row_off` is the element offset of the destination row (the same in out and aux0..2).
-template <int EPI, int BN_T>
+// Plain-store epilogue of one accumulator row: this thread owns the TMEM lane at `taddr`, BN_T fp32
+// columns, and writes them as bf16 to element offset `row_off` of p.out.  (Rows go to scattered
+// token positions here, and the store is hidden behind the long contraction of the GEMMs that use
+// it; the SwiGLU epilogues below, with up to four accesses per element, transpose through shared
+// memory instead.)
+template <int BN_T>
 __device__ __forceinline__ void epilogue_row(uint32_t taddr, const GemmParams& p, int64_t row_off, bool valid,
                                              int n_base, int part, int parts) {
   // this warp drains chunk range [part * CH / parts, (part + 1) * CH / parts) of the tile's columns
   const int n_out = p.n_out;
-  if constexpr (EPI == EPI_STORE || EPI == EPI_DSWIGLU) {
-    constexpr int CH = BN_T / 32;
+  constexpr int CH = BN_T / 32;
 #pragma unroll 1
-    for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
-      uint32_t v[32];
-      tmem_ld_32x32(taddr + c * 32, v);
-      tmem_ld_wait();
-      const int n0 = n_base + c * 32;
-      if (valid && n0 < n_out) {
+  for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + c * 32, v);
+    tmem_ld_wait();
+    const int n0 = n_base + c * 32;
+    if (valid && n0 < n_out) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (n0 + j * 8 < n_out) {
-            const int64_t off = row_off + n0 + j * 8;
-            float a[8];
+      for (int j = 0; j < 4; ++j) {
+        if (n0 + j * 8 < n_out) {
+          float a[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) a[e] = __uint_as_float(v[j * 8 + e]);
-            if constexpr (EPI == EPI_STORE) {
-              *reinterpret_cast<uint4*>(p.out + off) = pack_bf16x8(a);
-            } else {
-              float t1[8], t3[8], d1[8], d3[8];
-              unpack_bf16x8(*reinterpret_cast<const uint4*>(p.aux0 + off), t1);
-              unpack_bf16x8(*reinterpret_cast<const uint4*>(p.aux1 + off), t3);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const float sg = __frcp_rn(1.0f + __expf(-t1[e]));
-                d1[e] = a[e] * t3[e] * sg * (1.0f + t1[e] * (1.0f - sg));
-                d3[e] = a[e] * t1[e] * sg;
-              }
-              *reinterpret_cast<uint4*>(p.out + off) = pack_bf16x8(d1);
-              *reinterpret_cast<uint4*>(p.aux2 + off) = pack_bf16x8(d3);
-            }
-          }
-        }
-      }
-    }
-  } else {
-    constexpr int CH = BN_T / 64;
-#pragma unroll 1
-    for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
-      uint32_t g[32], u[32];
-      tmem_ld_32x32(taddr + c * 32, g);              // gate  (t1)
-      tmem_ld_32x32(taddr + BN_T / 2 + c * 32, u);   // up    (t3)
-      tmem_ld_wait();
-      const int n0 = n_base + c * 32;
-      if (valid && n0 < n_out) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (n0 + j * 8 < n_out) {
-            const int64_t off = row_off + n0 + j * 8;
-            float t1[8], t3[8], h[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              t1[e] = __uint_as_float(g[j * 8 + e]);
-              t3[e] = __uint_as_float(u[j * 8 + e]);
-            }
-            if constexpr (EPI == EPI_SWIGLU_SAVE) {
-              // H below is formed from the fp32 accumulators, exactly as in the inference epilogue (the
-              // training and inference forward give the same y); only the saved copies are rounded
-              *reinterpret_cast<uint4*>(p.aux0 + off) = pack_bf16x8(t1);
-              *reinterpret_cast<uint4*>(p.aux1 + off) = pack_bf16x8(t3);
-            }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) h[e] = silu_mul(t1[e], t3[e]);
-            *reinterpret_cast<uint4*>(p.out + off) = pack_bf16x8(h);
-          }
+          for (int e = 0; e < 8; ++e) a[e] = __uint_as_float(v[j * 8 + e]);
+          *reinterpret_cast<uint4*>(p.out + row_off + n0 + j * 8) = pack_bf16x8(a);
         }
       }
     }
@@ -343,6 +296,92 @@ __device__ __forceinline__ void epilogue_glu_staged(uint32_t taddr, const GemmPa
 #pragma unroll
     for (int e = 0; e < 32; ++e) t1[e] = silu_mul(t1[e], t3[e]);
     flush(t1, p.out, n0);
+  }
+}
+
+// dSwiGLU epilogue (FFN backward) with the same shared-memory transposition, for the two loads of
+// the saved pre-activations as well as for the two stores: four accesses per element, each of which
+// would otherwise touch 32 rows per instruction.
+template <int BN_T>
+__device__ __forceinline__ void epilogue_dswiglu_staged(uint32_t taddr, const GemmParams& p, long long row_off,
+                                                        int n_base, int part, int parts, uint8_t* stg, int lane) {
+  constexpr int CH = BN_T / 32;
+  const int pc = lane & 3;
+  long long ro[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) ro[i] = __shfl_sync(0xFFFFFFFFu, row_off, i * 8 + (lane >> 2));
+  uint8_t* mine = stg + lane * 64;
+  const int wsw = (lane >> 1) & 3;
+  // global loads of one chunk of a saved matrix: 8 rows x 64 bytes per instruction
+  auto load4 = [&](uint4 (&l)[4], const __nv_bfloat16* base, int n0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      l[i] = make_uint4(0, 0, 0, 0);
+      if (ro[i] >= 0 && n0 + pc * 8 < p.n_out) l[i] = *reinterpret_cast<const uint4*>(base + ro[i] + n0 + pc * 8);
+    }
+  };
+  // ... transposed through shared memory into this lane's row
+  auto spread = [&](float (&v)[32], const uint4 (&l)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i * 8 + (lane >> 2);
+      *reinterpret_cast<uint4*>(stg + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4)) = l[i];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a[8];
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(mine + ((j ^ wsw) << 4)), a);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[j * 8 + e] = a[e];
+    }
+    __syncwarp();
+  };
+  auto flush = [&](const float (&v)[32], __nv_bfloat16* base, int n0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] = v[j * 8 + e];
+      *reinterpret_cast<uint4*>(mine + ((j ^ wsw) << 4)) = pack_bf16x8(a);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i * 8 + (lane >> 2);
+      const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4));
+      if (ro[i] >= 0 && n0 + pc * 8 < p.n_out) *reinterpret_cast<uint4*>(base + ro[i] + n0 + pc * 8) = val;
+    }
+    __syncwarp();
+  };
+  const int c_begin = part * CH / parts, c_end = (part + 1) * CH / parts;
+  uint4 l1[4], l3[4];
+  load4(l1, p.aux0, n_base + c_begin * 32);
+  load4(l3, p.aux1, n_base + c_begin * 32);
+#pragma unroll 1
+  for (int c = c_begin; c < c_end; ++c) {
+    uint32_t acc[32];
+    tmem_ld_32x32(taddr + c * 32, acc);
+    const int n0 = n_base + c * 32;
+    float t1[32], t3[32];
+    spread(t1, l1);
+    spread(t3, l3);
+    if (c + 1 < c_end) {             // the next chunk's loads fly while this one is computed and stored
+      load4(l1, p.aux0, n0 + 32);
+      load4(l3, p.aux1, n0 + 32);
+    }
+    tmem_ld_wait();
+    if (n0 >= p.n_out) continue;   // warp-uniform
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float dh = __uint_as_float(acc[e]);
+      const float sg = __frcp_rn(1.0f + __expf(-t1[e]));
+      const float d1 = dh * t3[e] * sg * (1.0f + t1[e] * (1.0f - sg));
+      t3[e] = dh * t1[e] * sg;     // d3
+      t1[e] = d1;
+    }
+    flush(t1, p.out, n0);
+    flush(t3, p.aux2, n0);
   }
 }
 
@@ -631,8 +670,11 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       else if constexpr (epi_glu(EPI))
         epilogue_glu_staged<EPI, BN_T>(taddr, p, valid ? dst_row * p.ldo : -1ll, tc.nt * (BN_T / 2), part,
                                        epilogue_parts(), smem + TSTAGES * TSTAGE_BYTES + 256 + (warp - 2) * 2048, lane);
+      else if constexpr (EPI == EPI_DSWIGLU)
+        epilogue_dswiglu_staged<BN_T>(taddr, p, valid ? dst_row * p.ldo : -1ll, tc.nt * BN_T, part, epilogue_parts(),
+                                      smem + TSTAGES * TSTAGE_BYTES + 256 + (warp - 2) * 2048, lane);
       else
-        epilogue_row<EPI, BN_T>(taddr, p, dst_row * p.ldo, valid, tc.nt * (epi_glu(EPI) ? BN_T / 2 : BN_T), part, epilogue_parts());
+        epilogue_row<BN_T>(taddr, p, dst_row * p.ldo, valid, tc.nt * BN_T, part, epilogue_parts());
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -912,8 +954,11 @@ routed_gemm_pair_kernel(const __grid_constant__ AMaps am, const __grid_constant_
       else if constexpr (epi_glu(EPI))
         epilogue_glu_staged<EPI, BN>(taddr, p, valid ? dst_row * p.ldo : -1ll, tc.nt * N_PER_TILE, part,
                                      epilogue_parts(), smem + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * 2048, lane);
+      else if constexpr (EPI == EPI_DSWIGLU)
+        epilogue_dswiglu_staged<BN>(taddr, p, valid ? dst_row * p.ldo : -1ll, tc.nt * N_PER_TILE, part, epilogue_parts(),
+                                    smem + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * 2048, lane);
       else
-        epilogue_row<EPI, BN>(taddr, p, dst_row * p.ldo, valid, tc.nt * N_PER_TILE, part, epilogue_parts());
+        epilogue_row<BN>(taddr, p, dst_row * p.ldo, valid, tc.nt * N_PER_TILE, part, epilogue_parts());
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
@@ -1602,7 +1647,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   if (dev.cc_major != 10) return FFNK_ERR_DEVICE;
   const int n_per_tile = epi_glu(EPI) ? tile.bn / 2 : tile.bn;
   const int64_t n_tiles = (p.n_out + n_per_tile - 1) / n_per_tile;
-  constexpr int extra_smem = OUT_MODE == OUT_PEER ? PEER_STAGING : (epi_glu(EPI) ? GLU_STAGING : 0);
+  constexpr int extra_smem = OUT_MODE == OUT_PEER ? PEER_STAGING : ((epi_glu(EPI) || EPI == EPI_DSWIGLU) ? GLU_STAGING : 0);
   if (tile.pair) {
     int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
     if (pairs > usable_sms(dev) / 2) pairs = usable_sms(dev) / 2;
