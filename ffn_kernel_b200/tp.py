@@ -154,6 +154,21 @@ def all_reduce_gradients(tensors: Sequence[torch.Tensor], group=None, bucket_byt
     flush()
 
 
+def peer_block_rows(M: int, world: int) -> int:
+    """Rows per owner in the fused tensor-parallel path: token ``t`` belongs to rank ``t // rows``."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    return max(1, -(-M // world))
+
+
+def peer_owned_rows(M: int, rank: int, world: int) -> slice:
+    """Token range owned by ``rank`` (empty for trailing ranks when ``M`` is small)."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    rows = peer_block_rows(M, world)
+    return slice(min(M, rank * rows), min(M, (rank + 1) * rows))
+
+
 class PeerBlocks:
     """Per-rank block buffers, mapped into every rank, for ``masked_ffn_tp_fused``.
 
@@ -180,7 +195,7 @@ class PeerBlocks:
         if d % 8:
             raise ValueError("d must be a multiple of 8")
         self.M, self.d = M, d
-        self.rows = max(1, -(-M // self.world))
+        self.rows = peer_block_rows(M, self.world)
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.device = device
         self.buffers, self.pointers, self._handles = [], [], []
@@ -208,7 +223,7 @@ class PeerBlocks:
         dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group)
 
     def owned_rows(self) -> slice:
-        return slice(min(self.M, self.rank * self.rows), min(self.M, (self.rank + 1) * self.rows))
+        return peer_owned_rows(self.M, self.rank, self.world)
 
 
 def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gather: bool = True):

@@ -88,6 +88,20 @@ def test_row_shard_covers_everything():
             assert max(sizes) - min(sizes) <= 1
 
 
+def test_peer_owned_rows_partition_the_tokens():
+    # ownership in the fused tensor-parallel path: equal blocks of ceil(M / world) tokens, trailing ranks may be empty
+    for M in (0, 1, 7, 8, 9, 1000, 16384):
+        for world in (1, 2, 3, 8):
+            rows = tp.peer_block_rows(M, world)
+            assert rows >= 1 and rows * world >= M
+            parts = [tp.peer_owned_rows(M, r, world) for r in range(world)]
+            assert parts[0].start == 0 and parts[-1].stop == M
+            assert all(a.stop == b.start for a, b in zip(parts, parts[1:]))
+            assert all(p.start == min(M, r * rows) for r, p in enumerate(parts))
+    with pytest.raises(ValueError):
+        tp.peer_owned_rows(10, 3, 3)
+
+
 def test_h_shard_alignment_and_errors():
     assert tp.h_shard(11008, 7, 8) == slice(9632, 11008)
     assert all(tp.h_shard(11008, r, 8).start % 8 == 0 for r in range(8))
