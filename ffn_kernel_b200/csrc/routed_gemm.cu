@@ -1,5 +1,10 @@
-// Routed grouped GEMM for sm_100a: the forward GEMMs of MaskedLinear and MaskedFFN and the
-// dx GEMM of MaskedLinear backward.
+// Routed grouped GEMMs for sm_100a.  Kernels in this file:
+//   routed_gemm_kernel       single CTA, 128 x 256 (or 128 x 64) tiles: every forward and dx GEMM
+//   routed_gemm_pair_kernel  the same on CTA pairs (cta_group::2), 256 x 256 tiles
+//   wgrad_kernel             weight gradients (contraction over token rows), single CTA
+//   wgrad_pair_kernel        weight gradients on CTA pairs, operands in routed order
+// Epilogues: plain store (to token order, routed order, or straight into the memory of the GPU that
+// owns the row: OUT_PEER), SwiGLU, SwiGLU saving its pre-activations, dSwiGLU.
 //
 // The token rows of each modality are a compacted list (route.cu).  A CTA tile is 128 routed
 // rows of ONE modality times 256 accumulator columns, so a tile multiplies by exactly one
