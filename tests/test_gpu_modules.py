@@ -45,3 +45,24 @@ def test_ffn_module_forward_and_state_dict_names(dev):
     ref = O.masked_ffn(x.cpu().flatten(0, 1), *ws, mask.cpu().flatten())
     assert y.shape == (B, S, 128)
     assert O.max_rel_err(y.flatten(0, 1), ref) < TOL
+
+
+@pytest.mark.parametrize("tokens", [8, 300])
+def test_graphed_ffn_replays_match_eager(dev, tokens):
+    # decode-sized and GEMM-sized token counts; every replay must equal the eager forward on the same inputs
+    from ffn_kernel_b200 import GraphedMaskedFFN
+    torch.manual_seed(3)
+    mod = MaskedFFNModule(256, 520, device=dev)
+    graphed = GraphedMaskedFFN(mod, tokens)
+    for seed in range(3):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(tokens, 256, generator=g).to(torch.bfloat16).to(dev)
+        mask = (torch.rand(tokens, generator=g) < 0.5).to(dev)
+        y_graph = graphed(x, mask).clone()
+        with torch.no_grad():
+            y_eager = mod(x, mask)
+        check_status()
+        assert torch.equal(y_graph, y_eager)
+    with pytest.raises(RuntimeError):
+        graphed(torch.zeros(tokens + 1, 256, device=dev, dtype=torch.bfloat16),
+                torch.zeros(tokens + 1, device=dev, dtype=torch.bool))
