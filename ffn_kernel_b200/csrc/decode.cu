@@ -166,18 +166,25 @@ __global__ void __launch_bounds__(WARPS * 32) decode_phase_kernel(const DecodePa
   }
   if (!waited) pdl_wait_primary();
 
-  // sum the partial products of the warps in shared memory
+  // sum the partial products of the warps in shared memory, one warp after the other: the order of
+  // the fp32 additions is fixed, so the same inputs give the same bits on every run (shared-memory
+  // atomics would be a few hundred cycles cheaper and make the last bit depend on warp timing)
+#pragma unroll 1
+  for (int w = 0; w < WARPS; ++w) {
+    if (warp == w) {
 #pragma unroll
-  for (int gi = 0; gi < G; ++gi) {
-    if (gi < ngroups) {
+      for (int gi = 0; gi < G; ++gi) {
+        if (gi < ngroups) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        atomicAdd(&red[gi][lane][i], acc_a[gi][i]);
-        if constexpr (GATEUP) atomicAdd(&red[gi][lane][4 + i], acc_b[gi][i]);
+          for (int i = 0; i < 4; ++i) {
+            red[gi][lane][i] += acc_a[gi][i];
+            if constexpr (GATEUP) red[gi][lane][4 + i] += acc_b[gi][i];
+          }
+        }
       }
     }
+    __syncthreads();
   }
-  __syncthreads();
   for (int gi = warp; gi < ngroups; gi += WARPS) {
     // accumulator element i: row (g + 8 * (i >> 1)), token slot (2 t + (i & 1)) of the group
 #pragma unroll

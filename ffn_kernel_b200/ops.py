@@ -7,6 +7,9 @@ the reference leaves raising ``NotImplementedError`` (``ffn_kernel/ops.py:34-38`
 """
 from __future__ import annotations
 
+import threading
+
+import torch
 from torch.amp import custom_bwd, custom_fwd
 from torch.autograd import Function
 from torch.autograd.function import once_differentiable
@@ -17,6 +20,12 @@ from .linear import _bf16_linear_backward, _bf16_linear_forward
 from .route import route
 
 __all__ = ["MaskedLinear", "MaskedFFN"]
+
+# Whether gradients were being recorded when MaskedFFN.apply was called.  Inside Function.forward
+# grad mode is always off and ctx.needs_input_grad only says which inputs have requires_grad set
+# (true for every nn.Parameter, also under torch.no_grad()), so the caller's grad mode is noted
+# on the way in: inference under no_grad must not pay for the training forward.
+_call = threading.local()
 
 
 class MaskedLinear(Function):
@@ -49,10 +58,15 @@ class MaskedFFN(Function):
     it is implemented after the reference's own formulas (``README.md:159-172``): when any input
     requires a gradient, the forward keeps the routed activations and pre-activations."""
 
+    @classmethod
+    def apply(cls, *args, **kwargs):
+        _call.grad_enabled = torch.is_grad_enabled()
+        return super().apply(*args, **kwargs)
+
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, a, w1, w2, w3, u1, u2, u3, mask):
-        if any(ctx.needs_input_grad[:7]):
+        if getattr(_call, "grad_enabled", True) and any(ctx.needs_input_grad[:7]):
             y, ctx.saved = _bf16_ffn_train_forward(a, w1, w2, w3, u1, u2, u3, mask)
             return y
         ctx.saved = None

@@ -176,6 +176,24 @@ def test_backward_only_when_asked_for(dev):
     assert not y.requires_grad
 
 
+def test_no_grad_takes_the_inference_path_even_with_parameters(dev, monkeypatch):
+    # nn.Parameter weights have requires_grad set also under torch.no_grad(); the forward that keeps
+    # activations for a backward pass must not run then
+    import ffn_kernel_b200.ops as ops
+    called = []
+    real = ops._bf16_ffn_train_forward
+    monkeypatch.setattr(ops, "_bf16_ffn_train_forward", lambda *a: (called.append(1), real(*a))[1])
+    c = ffn_case(64, 64, 64, seed=1).to(dev)
+    args = list(c.apply_args())
+    args[1:7] = [w.detach().clone().requires_grad_(True) for w in args[1:7]]
+    with torch.no_grad():
+        y = MaskedFFN.apply(*args)
+    assert not called and not y.requires_grad
+    y = MaskedFFN.apply(*args)
+    assert called and y.requires_grad
+    check_status()
+
+
 def test_backward_full_size_rows_sampled(dev):
     # d = 1024 / h = 2048, M = 32768: dx on sampled rows (row independence) and a column block of dW
     M, d, h = 32768, 1024, 2048
