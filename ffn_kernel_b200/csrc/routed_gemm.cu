@@ -1908,8 +1908,10 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     if (e == cudaSuccess) e = cudaMemset2DAsync(db2, ld * 2, 0, cols * 2, rows, s);
     return cuda_status(e);
   }
-  if (!g || !a || !b1 || !b2 || !perm || !counts || !da) return FFNK_ERR_NULL;
-  if ((ldg & 7) || (lda & 7) || (ldda & 7) || ldg < N || lda < K || ldda < K ||
+  // a may be null when a_copy already holds it in routed order (left there by the forward pass)
+  const bool a_prepared = !a && g_copy && a_copy;
+  if (!g || (!a && !a_prepared) || !b1 || !b2 || !perm || !counts || !da) return FFNK_ERR_NULL;
+  if ((ldg & 7) || (ldda & 7) || ldg < N || ldda < K || (a && ((lda & 7) || lda < K)) ||
       (reinterpret_cast<uintptr_t>(da) & 15))
     return FFNK_ERR_ALIGN;
   const DeviceInfo& dev = device_info();
@@ -1931,7 +1933,7 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     int r;
     if (copies) {
       if ((r = permute_rows_launch(g, ldg, perm, counts, g_copy, N, M, N, 0, stream))) return r;
-      if ((r = permute_rows_launch(a, lda, perm, counts, a_copy, K, M, K, 0, stream))) return r;
+      if (a && (r = permute_rows_launch(a, lda, perm, counts, a_copy, K, M, K, 0, stream))) return r;
       if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], g_copy, N, copy_rows, N, BK, BM))) return r;
       for (int i = 0; i <= COPY_MAP; ++i)
         if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];

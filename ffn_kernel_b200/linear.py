@@ -114,11 +114,44 @@ def _bf16_linear_forward(a, b1, b2, mask, rt: Route | None = None):
     return c
 
 
-def _bf16_linear_backward(gd, a, b1, b2, mask, rt: Route | None = None):
-    """Returns (da, db1, db2); db1/db2 carry the strides of b1/b2 (``empty_like``,
-    ``ffn_kernel/linear.py:475``)."""
+def _bf16_linear_train_forward(a, b1, b2, mask, rt: Route | None = None):
+    """Forward pass for training at M >= 512: copies ``a`` into routed order once, multiplies from
+    the copy (the kernel of the FFN down projection: whole tiles of consecutive rows, results
+    scattered back to token order) and hands the copy to the backward pass, which would otherwise
+    make it again.  Returns ``(c, a_routed)``; ``a_routed`` is None when the ordinary forward ran."""
     a = _activation(a, "a")
     M, K = a.shape
+    N = b1.shape[1] if isinstance(b1, torch.Tensor) and b1.dim() == 2 else -1
+    b1, b2 = _weights((b1, b2), ("b1", "b2"), K, N)
+    _check_dims(K=K, N=N)
+    dev = a.device
+    with torch.cuda.device(dev):
+        a_routed = _copy_scratch(M, K, dev) if M > 0 else None
+    if a_routed is None:
+        return _bf16_linear_forward(a, b1, b2, mask, rt), None
+    L = lib()
+    with torch.cuda.device(dev):
+        c = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+        rt = _mask_route(mask, M, dev, rt)
+        st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
+        check("ffnk_permute_rows", L.ffnk_permute_rows(
+            a.data_ptr(), a.stride(0), rt.perm.data_ptr(), rt.counts.data_ptr(), a_routed.data_ptr(), K, M, K, sp))
+        check("ffnk_ffn_down", L.ffnk_ffn_down(
+            a_routed.data_ptr(), K, b1.data_ptr(), b2.data_ptr(), b1.stride(0), b1.stride(1), rt.perm.data_ptr(),
+            rt.counts.data_ptr(), c.data_ptr(), c.stride(0), M, N, K, st, sp))
+    maybe_check(dev)
+    return c, a_routed
+
+
+def _bf16_linear_backward(gd, a, b1, b2, mask, rt: Route | None = None, a_routed=None):
+    """Returns (da, db1, db2); db1/db2 carry the strides of b1/b2 (``empty_like``,
+    ``ffn_kernel/linear.py:475``).  ``a_routed``: the routed-order copy of ``a`` a training forward
+    left behind (``a`` itself is then not needed and may be None)."""
+    if a_routed is not None:
+        M, K = int(mask.shape[0]), int(a_routed.shape[1])
+    else:
+        a = _activation(a, "a")
+        M, K = a.shape
     N = b1.shape[1] if isinstance(b1, torch.Tensor) and b1.dim() == 2 else -1
     _require_cuda(gd, "grad")
     if tuple(gd.shape) != (M, N):
@@ -126,7 +159,7 @@ def _bf16_linear_backward(gd, a, b1, b2, mask, rt: Route | None = None):
     gd = _activation(gd, "grad")
     b1, b2 = _weights((b1, b2), ("b1", "b2"), K, N)
     _check_dims(K=K, N=N)
-    dev = a.device
+    dev = gd.device
     with torch.cuda.device(dev):
         da = torch.empty((M, K), device=dev, dtype=torch.bfloat16)
         db1, db2 = torch.empty_like(b1), torch.empty_like(b2)
@@ -136,9 +169,14 @@ def _bf16_linear_backward(gd, a, b1, b2, mask, rt: Route | None = None):
         if M == 0:
             return da, db1.zero_(), db2.zero_()
         rt = _mask_route(mask, M, dev, rt)
-        g_copy, a_copy = _copy_scratch(M, N, dev), _copy_scratch(M, K, dev)
+        if a_routed is not None:
+            g_copy, a_copy = torch.empty((a_routed.shape[0], N), device=dev, dtype=torch.bfloat16), a_routed
+            a_ptr, a_ld = None, K
+        else:
+            g_copy, a_copy = _copy_scratch(M, N, dev), _copy_scratch(M, K, dev)
+            a_ptr, a_ld = a.data_ptr(), a.stride(0)
         check("ffnk_linear_bwd", lib().ffnk_linear_bwd(
-            gd.data_ptr(), gd.stride(0), a.data_ptr(), a.stride(0), b1.data_ptr(), b2.data_ptr(),
+            gd.data_ptr(), gd.stride(0), a_ptr, a_ld, b1.data_ptr(), b2.data_ptr(),
             b1.stride(0), b1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(),
             da.data_ptr(), da.stride(0), db1.data_ptr(), db2.data_ptr(), _ptr(g_copy), _ptr(a_copy), M, N, K,
             status_word(dev).data_ptr(), stream_ptr(dev)))

@@ -16,7 +16,7 @@ from torch.autograd.function import once_differentiable
 
 from .ffn import (_bf16_ffn_backward, _bf16_ffn_forward, _bf16_ffn_fused_forward,  # noqa: F401  (re-exported)
                   _bf16_ffn_train_forward)
-from .linear import _bf16_linear_backward, _bf16_linear_forward
+from .linear import _bf16_linear_backward, _bf16_linear_forward, _bf16_linear_train_forward
 from .route import route
 
 __all__ = ["MaskedLinear", "MaskedFFN"]
@@ -31,22 +31,42 @@ _call = threading.local()
 class MaskedLinear(Function):
     """``MaskedLinear.apply(a, b1, b2, mask)``: ``a[m] @ b1`` where ``mask[m]`` else ``a[m] @ b2``."""
 
+    @classmethod
+    def apply(cls, *args, **kwargs):
+        _call.grad_enabled = torch.is_grad_enabled()
+        return super().apply(*args, **kwargs)
+
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, a, b1, b2, mask):
-        ctx.save_for_backward(a, mask)
         ctx.b1, ctx.b2 = b1, b2
         rt = route(mask) if a.shape[0] > 0 else None
         ctx.route = rt          # the backward pass reuses the routing lists
+        if getattr(_call, "grad_enabled", True) and any(ctx.needs_input_grad[:3]):
+            # a backward pass will follow: it gets the routed-order copy of a instead of a itself
+            c, a_routed = _bf16_linear_train_forward(a, b1, b2, mask, rt)
+            if a_routed is not None:
+                ctx.save_for_backward(mask, a_routed)
+                ctx.routed = True
+                return c
+            ctx.save_for_backward(a, mask)
+            ctx.routed = False
+            return c
+        ctx.save_for_backward(a, mask)
+        ctx.routed = False
         return _bf16_linear_forward(a, b1, b2, mask, rt)
 
     @staticmethod
     @once_differentiable
     @custom_bwd(device_type="cuda")
     def backward(ctx, grad):
-        a, mask = ctx.saved_tensors
         b1, b2 = ctx.b1, ctx.b2
-        da, db1, db2 = _bf16_linear_backward(grad, a, b1, b2, mask, ctx.route)
+        if ctx.routed:
+            mask, a_routed = ctx.saved_tensors
+            da, db1, db2 = _bf16_linear_backward(grad, None, b1, b2, mask, ctx.route, a_routed=a_routed)
+        else:
+            a, mask = ctx.saved_tensors
+            da, db1, db2 = _bf16_linear_backward(grad, a, b1, b2, mask, ctx.route)
         return da, db1, db2, None
 
 

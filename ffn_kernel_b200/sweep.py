@@ -202,6 +202,19 @@ def main():
         if a.bwd:
             t = timeit(lambda: _bf16_linear_backward(c.g, c.x, c.wv.T, c.wt.T, c.mask, rt), a.iters, a.warmup)
             emit(kernel="linear_bwd(dx+dW)", M=M, K=K, N=N, mask=a.mask, ms=t, tflops=4 * M * K * N / t / 1e9)
+            # the whole training step through the operator: routing, forward, backward (the forward's
+            # routed-order copy of the activations is reused by the backward)
+            from .ops import MaskedLinear
+            x = c.x.clone().requires_grad_(True)
+            wv, wt = c.wv.clone().requires_grad_(True), c.wt.clone().requires_grad_(True)
+
+            def train_step():
+                x.grad = wv.grad = wt.grad = None
+                MaskedLinear.apply(x, wv.T, wt.T, c.mask).backward(c.g)
+
+            t = timeit(train_step, a.iters, a.warmup)
+            emit(kernel="linear train step (apply + backward)", M=M, K=K, N=N, mask=a.mask, ms=t,
+                 tflops=6 * M * K * N / t / 1e9)
     elif a.what == "route":
         m = edge_mask(a.M, "bernoulli" if a.mask == "span" and a.M > (1 << 22) else a.mask, 0).to(dev)
         t = timeit(lambda: route(m), a.iters, a.warmup)

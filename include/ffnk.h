@@ -110,6 +110,9 @@ int ffnk_linear_fwd(const void* a, int64_t lda, const void* b1, const void* b2, 
  * tiles of consecutive rows: dx with the kernel of ffnk_ffn_down, the weight gradients on CTA
  * pairs (M=32768, K=N=4096: 1.82 ms against 2.12-2.29 ms without).  Without it the kernels
  * gather token rows themselves; worthwhile only for small M.
+ * a may be null when both scratch matrices are given and a_copy already holds a in routed order
+ * (ffnk_permute_rows in the forward pass, which can then run its GEMM as ffnk_ffn_down on that copy):
+ * the call then skips that copy.
  * ------------------------------------------------------------------------------------- */
 int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
                     int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm, const int32_t* counts, void* da,

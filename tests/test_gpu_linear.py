@@ -175,3 +175,22 @@ def test_scattered_masks_with_and_without_the_routed_copy(dev, kind, monkeypatch
             assert O.max_rel_err(got, ref) < TOL
         outs.append((y, *grads))
     assert torch.equal(outs[0][0], outs[1][0])        # forward rows are the same sums either way
+
+
+@pytest.mark.parametrize("M", [600, 4200])
+def test_training_forward_hands_its_routed_copy_to_the_backward(dev, M):
+    # through .apply with gradients on, the forward multiplies from a routed-order copy of a and the
+    # backward reuses it; the launcher called directly with a itself must give the same gradients
+    from ffn_kernel_b200.linear import _bf16_linear_backward, _bf16_linear_forward
+    c = linear_case(M, 264, 328, seed=M, mask=edge_mask(M, "span", seed=1), with_grad=True).to(dev)
+    x = c.x.clone().requires_grad_(True)
+    b1, b2 = c.wv.clone().requires_grad_(True), c.wt.clone().requires_grad_(True)
+    y = MaskedLinear.apply(x, b1.T, b2.T, c.mask)
+    y.backward(c.g)
+    y_inf = _bf16_linear_forward(c.x, c.wv.T, c.wt.T, c.mask)
+    da, db1, db2 = _bf16_linear_backward(c.g, c.x, c.wv.T, c.wt.T, c.mask)
+    check_status()
+    assert torch.equal(y.detach(), y_inf)
+    assert torch.equal(x.grad, da) and torch.equal(b1.grad.T, db1) and torch.equal(b2.grad.T, db2)
+    with torch.no_grad():
+        assert not MaskedLinear.apply(x, b1.T, b2.T, c.mask).requires_grad
