@@ -44,7 +44,7 @@ WORKLOADS = {
 METRIC = "routed_bf16_tflops_maskedffn_fwd"
 # DRAM bytes per launch of the gate/up GEMM (dram__bytes_read.sum + dram__bytes_write.sum) from the
 # one-pass ncu capture of that kernel at the full C4 size (1.24 GB read + 0.36 GB written)
-GATEUP_DRAM_BYTES = {"c4_ffn_d4096_h11008_m16384": 1.60e9}
+GATEUP_DRAM_BYTES = {"c4_ffn_d4096_h11008_m16384": 1.62e9}
 
 
 def measured_peaks():
