@@ -1564,27 +1564,29 @@ static int usable_sms(const DeviceInfo& dev) {
   return n < 2 ? 2 : n;
 }
 
-static int pick_group_m(int64_t k_len) {
+// Row tiles per super-tile.  One super-tile of A rows should stay in L2 while the weights stream past
+// it: about 32 MiB of A for single CTAs (128-row tiles), about 16 MiB for CTA pairs (256-row tiles).
+// Measured with `python -m ffn_kernel_b200.tune`: pairs at K=4096 (MaskedLinear backward, M=32768)
+// 8 or 16 row tiles 1.69 ms, 32 row tiles 1.74, 48 row tiles 1.79; pairs at K=2048 (down projection,
+// M=32768) 8-16 row tiles 0.103 ms, 64 row tiles 0.109; single CTAs at K=4096 (gate/up) 32 row tiles
+// 2.07 ms, 16 row tiles 2.12, 8 row tiles 2.28.
+static int pick_group_m(int64_t k_len, bool pair = false) {
   static const int forced = [] {
     const char* e = getenv("FFNK_GROUP_M");
     return e ? atoi(e) : 0;
   }();
   if (forced > 0) return forced;
-  // keep one super-tile of A rows (group_m x 128 rows x K) near 32 MiB so that it stays in L2
-  // while the weights stream past it
-  int64_t g = (32ll << 20) / (BM * k_len * 2);
+  int64_t g = pair ? (16ll << 20) / (2 * BM * k_len * 2) : (32ll << 20) / (BM * k_len * 2);
   if (g < 4) g = 4;
   if (g > 64) g = 64;
   return static_cast<int>(g);
 }
 
-// Tile table (replaces the reference's JSON lookup, ffn_kernel/utils.py:3-5): CTA pairs with
-// 256-row tiles once there are enough rows to fill them, single CTAs with 128-row tiles below.
-// FFNK_PAIR=0/1 overrides the choice for experiments.
 // Tile table (replaces the reference's JSON lookup, ffn_kernel/utils.py:3-5).
 //   pair   : CTA pairs, 256-row tiles.  Measured at d=4096/h=11008, M=16384: +4 % when A arrives as one
-//            box per tile and the epilogue is a plain store (down projection), -3 % under the
-//            two-weight SwiGLU tile, so it is used for the former only, from M = 4096.
+//            box per tile and the epilogue is a plain store (down projection), -1...3 % under the
+//            two-weight SwiGLU tile, so from M = 4096 it is used for the former, and for the latter
+//            only when the contraction is at most 2048 long.
 //   narrow : single CTAs with 64 accumulator columns, for problems with so few row tiles that 256-wide
 //            tiles would leave most SMs idle (small M: the weights then stream through 4x as many CTAs).
 //   else   : single CTAs, 128 x 256 tiles.
@@ -1599,11 +1601,16 @@ static int env_flag(const char* name) {
   return e ? atoi(e) : -1;
 }
 
-static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool k_major_weights) {
+static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool k_major_weights,
+                            int64_t k_len = int64_t(1) << 30) {
   static const int force_pair = env_flag("FFNK_PAIR");
   static const int force_narrow = env_flag("FFNK_NARROW");
   TileChoice t{false, BN};
-  const bool pair = force_pair >= 0 ? force_pair != 0 : (M >= 4096 && a_mode == A_ROUTED && !epi_glu(epi));
+  // two-weight (SwiGLU) tiles go to pairs only when the contraction is short: there the MMA issuer
+  // waits for operands and the 32 KiB k-steps of a pair help (d=1024: gate/up 0.221 -> 0.214 ms);
+  // at d=4096 single CTAs measured a percent or two faster
+  const bool pair = force_pair >= 0 ? force_pair != 0
+                                    : (M >= 4096 && a_mode == A_ROUTED && (!epi_glu(epi) || k_len <= 2048));
   if (pair) {
     t.pair = true;
     return t;
@@ -1626,6 +1633,8 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   const int64_t n_tiles = (p.n_out + n_per_tile - 1) / n_per_tile;
   constexpr int extra_smem = EPI == EPI_STORE ? STORE_STAGING : GLU_STAGING;
   if (tile.pair) {
+    GemmParams pp = p;
+    pp.group_m = pick_group_m(static_cast<int64_t>(p.k_len) + p.k_len1, true);
     int64_t pairs = ((M + PAIR_BM - 1) / PAIR_BM + 1) * n_tiles;
     if (pairs > usable_sms(dev) / 2) pairs = usable_sms(dev) / 2;
     if (pairs < 1) pairs = 1;
@@ -1644,7 +1653,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
       attr[0].val.clusterDim.z = 1;
       cfg.attrs = attr;
       cfg.numAttrs = 1;
-      return cuda_status(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB[0], tmB[1], tmB[2], tmB[3], p));
+      return cuda_status(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB[0], tmB[1], tmB[2], tmB[3], pp));
     };
     return b_mn ? go(routed_gemm_pair_kernel<A_MODE, EPI, OUT_MODE, true>)
                 : go(routed_gemm_pair_kernel<A_MODE, EPI, OUT_MODE, false>);
@@ -1784,7 +1793,7 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
   bool mn = false, mn_i = false;
   const void* ws[4] = {w1, w3, u1, u3};
   const TileChoice tile = pick_tile(M, h, routed_in ? A_ROUTED : A_GATHER, EPI_SWIGLU,
-                                    weights_k_major(w_stride_k, w_stride_n, d));
+                                    weights_k_major(w_stride_k, w_stride_n, d), d);
   for (int i = 0; i < 4; ++i) {
     if ((r = weight_map(&tmB[i], WeightView{ws[i], w_stride_k, w_stride_n, d, h}, &mn_i, tile.bn / 2))) return r;
     mn = mn_i;
@@ -1979,7 +1988,7 @@ extern "C" int ffnk_ffn_forward_train(const void* x, int64_t ldx, const void* w1
       if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
     bool mn = false, mn_i = false;
     const void* ws[4] = {w1, w3, u1, u3};
-    const TileChoice tile = pick_tile(M, h, A_ROUTED, EPI_SWIGLU_SAVE, weights_k_major(w13_stride_k, w13_stride_n, d));
+    const TileChoice tile = pick_tile(M, h, A_ROUTED, EPI_SWIGLU_SAVE, weights_k_major(w13_stride_k, w13_stride_n, d), d);
     for (int i = 0; i < 4; ++i) {
       if ((r = weight_map(&tmB[i], WeightView{ws[i], w13_stride_k, w13_stride_n, d, h}, &mn_i, tile.bn / 2))) return r;
       mn = mn_i;
