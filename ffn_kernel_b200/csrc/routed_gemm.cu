@@ -1586,7 +1586,7 @@ static int pick_group_m(int64_t k_len, bool pair = false) {
 //   pair   : CTA pairs, 256-row tiles.  Measured at d=4096/h=11008, M=16384: +4 % when A arrives as one
 //            box per tile and the epilogue is a plain store (down projection), -1...3 % under the
 //            two-weight SwiGLU tile, so from M = 4096 it is used for the former, and for the latter
-//            only when the contraction is at most 2048 long.
+//            only from M = 16384 and when the weights fit in L2.
 //   narrow : single CTAs with 64 accumulator columns, for problems with so few row tiles that 256-wide
 //            tiles would leave most SMs idle (small M: the weights then stream through 4x as many CTAs).
 //   else   : single CTAs, 128 x 256 tiles.
@@ -1606,11 +1606,14 @@ static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool 
   static const int force_pair = env_flag("FFNK_PAIR");
   static const int force_narrow = env_flag("FFNK_NARROW");
   TileChoice t{false, BN};
-  // two-weight (SwiGLU) tiles go to pairs only when the contraction is short: there the MMA issuer
-  // waits for operands and the 32 KiB k-steps of a pair help (d=1024: gate/up 0.221 -> 0.214 ms);
-  // at d=4096 single CTAs measured a percent or two faster
+  // Two-weight (SwiGLU) tiles go to pairs only when the four weights (8 d h bytes) stay in L2 and there
+  // are many row tiles: the GEMM is then bound by L2 -> SM traffic, which a pair cuts by a third
+  // (M=32768 d=1024 h=2048: 0.221 -> 0.214 ms; M=16384 d=4096 h=1376: 0.279 -> 0.257 ms).  With weights
+  // streaming from DRAM single CTAs are a percent or two faster (d=4096 h=11008), and at M=4099
+  // (d=1024 h=2816) pairs lose 14 %.
+  const bool glu_pair = M >= 16384 && k_len * n_out <= (int64_t(8) << 20);
   const bool pair = force_pair >= 0 ? force_pair != 0
-                                    : (M >= 4096 && a_mode == A_ROUTED && (!epi_glu(epi) || k_len <= 2048));
+                                    : (M >= 4096 && a_mode == A_ROUTED && (!epi_glu(epi) || glu_pair));
   if (pair) {
     t.pair = true;
     return t;
