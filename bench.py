@@ -459,9 +459,9 @@ def run_ours(args):
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         rows = min(args.cpu_sample_rows, M)
-        tf, sec = cpu_reference_rate(case_cpu, rows, steps=3, warmup=1)
+        tf, sec = cpu_reference_rate(case_cpu, rows, steps=5, warmup=1)
         cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-               "sample": f"first {rows} of {M} tokens, full weights, median of 3 passes ({sec:.2f} s each); torch CPU "
+               "sample": f"first {rows} of {M} tokens, full weights, median of 5 passes ({sec:.2f} s each); torch CPU "
                          "bf16, both branches dense then mask-selected as the reference module does"}
 
     if rank == 0:
@@ -497,7 +497,8 @@ def main():
     ap.add_argument("--skip-tp", action="store_true", help="do not add the tensor-parallel timing to a dp run")
     ap.add_argument("--chunks", type=int, default=1,
                     help="token chunks per step in tp mode (>1 overlaps all-reduce with GEMMs; measured slower)")
-    ap.add_argument("--cpu-sample-rows", type=int, default=1024)
+    ap.add_argument("--cpu-sample-rows", type=int, default=8192,
+                    help="tokens per CPU pass (cpu_baseline and --impl reference): about 10-20 s of host work per run")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--traffic-bytes", type=float, default=None,
