@@ -413,6 +413,7 @@ __device__ __forceinline__ void epilogue_rows_staged(uint32_t taddr, const GemmP
   }
 }
 
+// BN_T = 128 (6 stages of 32 KiB) sits between the two.
 // BN_T = 256 is the throughput tile; BN_T = 64 (K-major weights only) spreads a problem with few row
 // tiles over more SMs: 8 stages of 24 KiB, four times as many column tiles.
 template <int A_MODE, int EPI, int OUT_MODE, bool B_MN, int BN_T>
@@ -420,10 +421,11 @@ __global__ void __launch_bounds__(GEMM_THREADS_MAX, 1)
 routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUtensorMap tmBv0,
                    const __grid_constant__ CUtensorMap tmBv1, const __grid_constant__ CUtensorMap tmBt0,
                    const __grid_constant__ CUtensorMap tmBt1, const GemmParams p) {
-  static_assert(BN_T == 256 || (BN_T == 64 && !B_MN), "64-column tiles exist for K-major weights only");
+  static_assert(BN_T == 256 || ((BN_T == 128 || BN_T == 64) && !B_MN),
+                "128- and 64-column tiles exist for K-major weights only");
   constexpr int TB_BYTES = BN_T * BK * 2;
   constexpr int TSTAGE_BYTES = A_BYTES + TB_BYTES;
-  constexpr int TSTAGES = (BN_T == 256) ? STAGES : 8;
+  constexpr int TSTAGES = (BN_T == 256) ? STAGES : (BN_T == 128 ? 6 : 8);   // 192 KiB of stages either way
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + TSTAGES * TSTAGE_BYTES);
@@ -1590,7 +1592,7 @@ static int pick_group_m(int64_t k_len, bool pair = false) {
 //   narrow : single CTAs with 64 accumulator columns, for problems with so few row tiles that 256-wide
 //            tiles would leave most SMs idle (small M: the weights then stream through 4x as many CTAs).
 //   else   : single CTAs, 128 x 256 tiles.
-// FFNK_PAIR=0/1 and FFNK_NARROW=0/1 override the choice for experiments.
+// FFNK_PAIR=0/1 and FFNK_NARROW=0/1/2 (256-, 64-, 128-column tiles) override the choice for experiments.
 struct TileChoice {
   bool pair;
   int bn;   // accumulator columns per tile
@@ -1618,10 +1620,25 @@ static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool 
     t.pair = true;
     return t;
   }
-  const int64_t n_per_tile = epi_glu(epi) ? BN / 2 : BN;
-  const int64_t wide_tiles = ((M + BM - 1) / BM + 1) * ((n_out + n_per_tile - 1) / n_per_tile);
-  const bool narrow = force_narrow >= 0 ? force_narrow != 0 : wide_tiles < device_info().sm_count;
-  if (narrow && k_major_weights) t.bn = 64;
+  if (!k_major_weights || force_narrow == 0) return t;
+  if (force_narrow == 1 || force_narrow == 2) {
+    t.bn = force_narrow == 1 ? 64 : 128;
+    return t;
+  }
+  // Few row tiles: narrower column tiles put more CTAs to work.  Estimate = waves on the SMs times the
+  // bytes one CTA pulls per k-step (A 16 KiB + 128 B per accumulator column); the widest tile wins ties.
+  const int sms = device_info().sm_count;
+  const int64_t m_tiles = (M + BM - 1) / BM + 1;
+  int64_t best = -1;
+  for (int bn : {256, 128, 64}) {
+    const int64_t n_per_tile = epi_glu(epi) ? bn / 2 : bn;
+    const int64_t tiles = m_tiles * ((n_out + n_per_tile - 1) / n_per_tile);
+    const int64_t est = ((tiles + sms - 1) / sms) * (16384 + 128 * bn);
+    if (best < 0 || est < best) {
+      best = est;
+      t.bn = bn;
+    }
+  }
   return t;
 }
 
@@ -1672,6 +1689,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
     return cuda_status(cudaGetLastError());
   };
   if (tile.bn == 64) return go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false, 64>);
+  if (tile.bn == 128) return go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false, 128>);
   return b_mn ? go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, true, BN>)
               : go(routed_gemm_kernel<A_MODE, EPI, OUT_MODE, false, BN>);
 }
