@@ -28,7 +28,8 @@ VARIANTS = [
     ("CTA pairs everywhere", {"FFNK_PAIR": "1"}),
     ("single CTAs everywhere", {"FFNK_PAIR": "0"}),
     ("128x64 tiles", {"FFNK_NARROW": "1"}),
-    ("no 128x64 tiles", {"FFNK_NARROW": "0"}),
+    ("128x128 tiles", {"FFNK_NARROW": "2"}),
+    ("128x256 tiles only", {"FFNK_NARROW": "0"}),
     ("x copied to routed order first", {"FFNK_PERMUTE": "1"}),
     ("rows gathered in the gate/up GEMM", {"FFNK_PERMUTE": "0"}),
     ("4 epilogue warps", {"FFNK_EPI_WARPS": "4"}),
