@@ -87,3 +87,17 @@ def test_reference_import_surface():
     import ffn_kernel_b200
     assert ffn_kernel.MaskedLinear is ffn_kernel_b200.MaskedLinear
     assert ffn_kernel.MaskedFFN is ffn_kernel_b200.MaskedFFN
+
+
+def test_header_is_valid_c99_and_cxx():
+    # the boundary is a C ABI: the header must compile as C (no C++-isms) and as C++ (extern "C" guards)
+    import shutil
+    import subprocess
+    header = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "ffnk.h")
+    for compiler, flags in (("gcc", ["-std=c99", "-x", "c"]), ("g++", ["-std=c++17", "-x", "c++"])):
+        exe = shutil.which(compiler)
+        if exe is None:
+            pytest.skip(f"{compiler} not installed")
+        res = subprocess.run([exe, *flags, "-Wall", "-Werror", "-pedantic", "-fsyntax-only", header],
+                             capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
