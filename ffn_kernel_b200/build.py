@@ -65,32 +65,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         list(ex.map(run, jobs))
     if jobs or force or _stale(LIB, objs):
         run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs])
-    build_c_host(force)
     return LIB
-
-
-C_HOST_SRC = os.path.join(os.path.dirname(PKG), "tests", "cabi_host.c")
-C_HOST = os.path.join(LIBDIR, "cabi_host")
-
-
-def build_c_host(force: bool = False) -> str | None:
-    """The plain-C host of the GPU test suite (tests/cabi_host.c): gcc -std=c99 against include/ffnk.h,
-    linked with libffnk.so and the CUDA runtime.  Skipped when the source or gcc is missing."""
-    gcc = shutil.which("gcc")
-    if not gcc or not os.path.exists(C_HOST_SRC):
-        return None
-    header = os.path.join(os.path.dirname(PKG), "include", "ffnk.h")
-    if not (force or _stale(C_HOST, [C_HOST_SRC, header, LIB])):
-        return C_HOST
-    cuda = os.path.dirname(os.path.dirname(_nvcc()))
-    cmd = [gcc, "-std=c99", "-O1", "-Wall", "-Werror", C_HOST_SRC, "-I", os.path.dirname(header),
-           "-I", os.path.join(cuda, "include"), "-L", LIBDIR, "-lffnk", "-L", os.path.join(cuda, "lib64"), "-lcudart",
-           "-lm", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64"), "-o", C_HOST]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode:
-        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
-        raise RuntimeError("building tests/cabi_host.c failed")
-    return C_HOST
 
 
 if __name__ == "__main__":

@@ -129,6 +129,7 @@ extern "C" const char* ffnk_status_string(int code) {
     case FFNK_ERR_TENSORMAP: return "tensor map rejected by the driver";
     case FFNK_ERR_DEVICE: return "device is not compute capability 10.x";
     case FFNK_ERR_CAPACITY: return "problem exceeds the fixed capacity of the no-allocation entry point";
+    case FFNK_ERR_CAPTURE: return "first call on this device must be made outside stream capture";
     case ST_TIMEOUT_PRODUCER: return "device: TMA producer wait expired";
     case ST_TIMEOUT_MMA_FULL: return "device: MMA wait for operands expired";
     case ST_TIMEOUT_MMA_TMEM: return "device: MMA wait for accumulator expired";

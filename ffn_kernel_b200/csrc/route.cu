@@ -513,10 +513,13 @@ constexpr int64_t kNoAllocWords = 2 + (kNoAllocMaxTokens + kRouteTile - 1) / kRo
 constexpr int64_t kNoAllocWordsPadded = ((kNoAllocWords + 63) / 64) * 64;
 
 static __device__ __align__(256) uint32_t g_route_scratch[kNoAllocWordsPadded];
+// the workspace layout of route_launch is [run total][one word per tile][finished tiles]
+static_assert(kNoAllocWordsPadded >= (kNoAllocMaxTokens + kRouteTile - 1) / kRouteTile + 2,
+              "the fixed array must hold the scan state of a mask of FFNK_ROUTE_NOALLOC_MAX_TOKENS tokens");
 
 // In host code `g_route_scratch` is only a handle for the runtime, not an address a kernel can
 // use: the device address is asked for once per device (with that device current) and cached.
-static int route_scratch_address(uint32_t** out) {
+static int route_scratch_address(uint32_t** out, cudaStream_t stream) {
   static std::mutex mu;
   static uint32_t* addr[64] = {};
   int dev = -1;
@@ -525,6 +528,11 @@ static int route_scratch_address(uint32_t** out) {
   if (dev < 0 || dev >= 64) return FFNK_ERR_DEVICE;
   std::lock_guard<std::mutex> lock(mu);
   if (addr[dev] == nullptr) {
+    // The lookup is not a stream operation; made while `stream` is being captured it could break the
+    // capture and the caller would see only an opaque runtime error.  Refuse instead, launching nothing.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+      return FFNK_ERR_CAPTURE;
     uint32_t* ptr = nullptr;
     e = cudaGetSymbolAddress((void**)&ptr, g_route_scratch);
     if (e != cudaSuccess) return cuda_status(e);
@@ -550,7 +558,7 @@ extern "C" int ffnk_route_noalloc(const void* mask, int64_t M, int32_t* perm, in
   if (!mask || !perm) return FFNK_ERR_NULL;
   if (reinterpret_cast<uintptr_t>(perm) & 15) return FFNK_ERR_ALIGN;
   uint32_t* scratch = nullptr;
-  const int r = route_scratch_address(&scratch);
+  const int r = route_scratch_address(&scratch, stream);
   if (r) return r;
   // the array still holds the previous call's tile states: route_launch clears the part this call uses
   return route_launch(static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm, counts, scratch, status,

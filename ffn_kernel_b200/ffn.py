@@ -102,7 +102,7 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
             if mask.dim() != 1 or mask.shape[0] != M or mask.device != dev:
                 raise RuntimeError(f"mask must have shape [{M}] on {dev}")
             m8 = mask.contiguous()
-            inter = torch.empty((M, h), device=dev, dtype=torch.float32)
+            inter = torch.empty((M, h), device=dev, dtype=torch.bfloat16)
             check("ffnk_ffn_decode", L.ffnk_ffn_decode(
                 x.data_ptr(), x.stride(0), w1.data_ptr(), w2.data_ptr(), w3.data_ptr(), u1.data_ptr(),
                 u2.data_ptr(), u3.data_ptr(), w1.stride(0), w1.stride(1), w2.stride(0), w2.stride(1),

@@ -42,8 +42,14 @@ def _weight_ok(w: torch.Tensor) -> bool:
 
 def _weights(ws, names, K, N):
     """Logical [K, N] bf16 weights, either the ``nn.Linear.weight.T`` view (stride_k == 1) or
-    contiguous (stride_n == 1).  All weights of one call must share one layout; anything
-    else is copied to contiguous [K, N]."""
+    contiguous (stride_n == 1); both are multiplied from their own storage, no copy is made.
+
+    The kernels take one pair of strides per call (as the reference's launchers do: they pass the
+    first weight's strides for all of them, ``ffn_kernel/linear.py:482``, ``ffn_kernel/ffn.py:551``,
+    and compute garbage when the others differ).  Weights of one call that do NOT share a layout,
+    or a weight that is neither K-major nor N-major with 16-byte aligned rows, are therefore copied
+    to contiguous [K, N] here -- the one place a weight is ever copied, and never on the layouts
+    the reference's callers use."""
     for w, n in zip(ws, names):
         _require_cuda(w, n)
         if w.dim() != 2 or tuple(w.shape) != (K, N):

@@ -19,7 +19,8 @@
  *   - A weight is the logical [K, N] matrix the reference's operators receive (b1/b2, w*, u*).
  *     It is described by its element strides (stride_k, stride_n); exactly one of them must
  *     be 1.  stride_k == 1 is the `nn.Linear.weight.T` view (storage [N, K]); stride_n == 1
- *     is a contiguous [K, N] matrix.  No transposed copy is ever made.
+ *     is a contiguous [K, N] matrix.  This library never copies or transposes a weight; all
+ *     weights of one call share one pair of strides (anything else is the caller's to repack).
  *   - mask: one byte per token, non-zero = first weight set ("visual"), zero = second ("text")
  *     (ffn_kernel/linear.py:137-140).
  *   - Routing lists (`perm`, `counts`) are produced by ffnk_route() on the same stream.
@@ -41,6 +42,7 @@ extern "C" {
 #define FFNK_ERR_TENSORMAP (-6) /* the driver rejected a tensor map */
 #define FFNK_ERR_DEVICE (-7)    /* the current device is not compute capability 10.x */
 #define FFNK_ERR_CAPACITY (-8)  /* the problem exceeds the fixed capacity of a no-allocation entry point */
+#define FFNK_ERR_CAPTURE (-9)   /* first call of a no-allocation entry point on this device made during stream capture */
 
 /* Library version (major * 100 + minor). */
 int ffnk_version(void);
@@ -77,7 +79,9 @@ int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* counts, void
  *     calls that may run on the GPU at the same time -- different streams -- race.  Issue them
  *     on one stream, or order them with events.
  *   - The first call on each device looks up the array's device address; make that first call
- *     outside any stream capture.  Nothing is allocated or freed, then or later.
+ *     outside any stream capture (an empty mask will not do: it returns before the lookup).  A first
+ *     call that arrives while `stream` is being captured returns FFNK_ERR_CAPTURE and launches nothing.
+ *     Nothing is allocated or freed, then or later.
  * ------------------------------------------------------------------------------------- */
 #define FFNK_ROUTE_NOALLOC_MAX_TOKENS 16777216 /* 2^24 tokens */
 int ffnk_route_noalloc(const void* mask, int64_t M, int32_t* perm, int32_t* counts, int32_t* status, void* stream);
@@ -222,7 +226,7 @@ int ffnk_ffn_forward(const void* x, int64_t ldx, const void* w1, const void* w2,
  * of the reference's README.md:159-172.
  *
  * rows = ffnk_route_capacity(M) + 512.  The caller owns, and keeps alive between the two calls:
- *   perm int32[2*cap], counts int32[4]      routing lists (written by the forward)
+ *   perm int32[2*cap], counts int32[8]      routing lists (written by the forward, as by ffnk_route)
  *   xr  bf16 [rows, d]                      x in routed order
  *   t1, t3, hid bf16 [rows, h]              gate and up pre-activations, and silu(t1) * t3
  * Backward scratch: gr bf16 [rows, d], dt1 and dt3 bf16 [rows, h].  The six weight gradients are

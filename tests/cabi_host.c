@@ -163,6 +163,36 @@ int main(void) {
       y_ref[m * D + c] = acc;
     }
   }
+  /* ---------------- training forward: counts is int32[8] (as for ffnk_route); the word behind it must stay untouched,
+   * and y must equal the inference forward's y bit for bit */
+  {
+    const size_t rows = (size_t)cap + 512;
+    void *tcounts, *txr, *tt1, *tt3, *thid, *ty;
+    static int32_t guard_in[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0x5EED5EED}, guard_out[9];
+    static uint16_t y_train[M * D];
+    CHECK_CUDA(cudaMalloc(&tcounts, sizeof guard_in));
+    CHECK_CUDA(cudaMemcpy(tcounts, guard_in, sizeof guard_in, cudaMemcpyHostToDevice));
+    CHECK_CUDA(cudaMalloc(&txr, rows * D * 2));
+    CHECK_CUDA(cudaMalloc(&tt1, rows * H * 2));
+    CHECK_CUDA(cudaMalloc(&tt3, rows * H * 2));
+    CHECK_CUDA(cudaMalloc(&thid, rows * H * 2));
+    CHECK_CUDA(cudaMalloc(&ty, (size_t)M * D * 2));
+    CHECK_FFNK(ffnk_ffn_forward_train(dx, D, dw[0], dw[1], dw[2], dw[3], dw[4], dw[5], 1, D, 1, H, dmask, (int32_t*)dperm,
+                                      (int32_t*)tcounts, dscan, txr, tt1, tt3, thid, ty, D, M, D, H, (int32_t*)dstatus,
+                                      NULL));
+    CHECK_FFNK(ffnk_read_status((int32_t*)dstatus, 1, NULL));
+    CHECK_CUDA(cudaMemcpy(guard_out, tcounts, sizeof guard_out, cudaMemcpyDeviceToHost));
+    CHECK_CUDA(cudaMemcpy(y_train, ty, sizeof y_train, cudaMemcpyDeviceToHost));
+    if (guard_out[8] != 0x5EED5EED || guard_out[0] != mv || guard_out[1] != mt || guard_out[4] != runs) {
+      fprintf(stderr, "cabi_host: training forward wrote outside counts[8] or wrong counts (guard %x)\n", guard_out[8]);
+      return 1;
+    }
+    if (memcmp(y_train, y16, sizeof y16) != 0) {
+      fprintf(stderr, "cabi_host: training forward and inference forward disagree\n");
+      return 1;
+    }
+  }
+
   const double e_lin = max_rel_err(lin16, lin_ref, (size_t)M * H);
   const double e_ffn = max_rel_err(y16, y_ref, (size_t)M * D);
   printf("cabi_host: routing exact (Mv=%d Mt=%d runs=%d), linear %.2e, ffn %.2e\n", mv, mt, runs, e_lin, e_ffn);

@@ -48,6 +48,20 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(dev):
         assert torch.equal(perm_a[:mv].long(), torch.nonzero(mask).flatten())
 
 
+def test_full_capacity_then_a_short_mask(dev):
+    """The longest mask the fixed array can serve (2^24 tokens: the two-kernel count + scatter path, which
+    uses every word of the array), immediately followed by a short multi-tile mask on the same stream."""
+    for M, kind in ((MAX_TOKENS, "bernoulli"), (70001, "bernoulli")):
+        mask = edge_mask(M, kind, seed=3).to(dev)
+        (perm_a, counts_a), (perm_b, counts_b) = _route_both(mask, dev)
+        assert torch.equal(counts_a, counts_b)
+        mv, mt, cap, m = counts_a.tolist()[:4]
+        assert m == M and mv + mt == M
+        assert torch.equal(perm_a[:mv], perm_b[:mv])
+        assert torch.equal(perm_a[cap:cap + mt], perm_b[cap:cap + mt])
+        assert int(perm_a[:mv].long().sum()) == int(torch.nonzero(mask).flatten().sum())
+
+
 def test_capacity_and_argument_errors(dev):
     L = lib()
     st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
