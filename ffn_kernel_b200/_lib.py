@@ -38,6 +38,9 @@ SIGNATURES = {
                                        POINTER(c_void_p), c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
                                        c_void_p, c_void_p]),
     "ffnk_sum_row_blocks": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
+    "ffnk_peer_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_int32, c_int64, c_void_p, c_void_p]),
+    "ffnk_sum_row_blocks_to_peers": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, POINTER(c_void_p), c_int,
+                                             c_int64, c_int64, c_int, c_void_p]),
     "ffnk_decode_max_tokens": (c_int, []),
     "ffnk_ffn_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,

@@ -137,6 +137,7 @@ extern "C" const char* ffnk_status_string(int code) {
     case ST_TIMEOUT_SCAN: return "device: routing scan look-back expired";
     case ST_TIMEOUT_TEST: return "device: self-test wait expired (expected)";
     case ST_TIMEOUT_PEER: return "device: wait on partner CTA expired";
+    case ST_TIMEOUT_RANK: return "device: barrier wait for another rank expired";
     default: return code <= -1000 ? "CUDA runtime error, code = -(1000 + cudaError_t)" : "unknown code";
   }
 }

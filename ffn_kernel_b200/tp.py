@@ -170,14 +170,22 @@ def peer_owned_rows(M: int, rank: int, world: int) -> slice:
 
 
 class PeerBlocks:
-    """Per-rank block buffers, mapped into every rank, for ``masked_ffn_tp_fused``.
+    """Peer-mapped buffers of one tensor-parallel group for ``masked_ffn_tp_fused``.
 
-    Rank ``r`` owns tokens ``[r * rows, (r + 1) * rows)`` with ``rows = ceil(M / world)``.  Its buffer
-    holds ``world`` row blocks of ``rows x d`` bf16; block ``s`` receives rank ``s``'s partial result
-    for the owner's rows.  Two buffers alternate from call to call, so the writes of step ``k + 1``
-    never touch what an owner may still be summing from step ``k`` (one barrier per step is
-    enough).  Construction is collective: every rank of ``group`` must create it, in the same order.
+    Rank ``r`` owns tokens ``[r * rows, (r + 1) * rows)`` with ``rows = ceil(M / world)`` (per token
+    chunk when the call is chunked).  Every rank holds, in symmetric memory mapped into all ranks:
+
+    * block buffers: ``world`` row blocks, block ``s`` receiving rank ``s``'s partial result for the
+      owner's rows (written by the peers' down projections);
+    * output matrices ``[M, d]``: every owner stores its summed rows into the output of every rank;
+    * one flag array for ``barrier()``.
+
+    Two block buffers and two outputs alternate from call to call: the result of a call stays valid
+    until the call after the next one on the same group.  Construction is collective: every rank of
+    ``group`` must create it, in the same order.
     """
+
+    MAX_CHUNKS = 8
 
     def __init__(self, M: int, d: int, group=None, device=None, buffers: int = 2):
         import ctypes
@@ -198,43 +206,88 @@ class PeerBlocks:
         self.rows = peer_block_rows(M, self.world)
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.device = device
-        self.buffers, self.pointers, self._handles = [], [], []
-        for _ in range(buffers):
-            t = symm.empty(self.world * self.rows * d, dtype=torch.bfloat16, device=device)
+        self._handles = []
+
+        def mapped(numel, dtype):
+            t = symm.empty(numel, dtype=dtype, device=device)
             hdl = symm.rendezvous(t, group)
             ptrs = [int(p) for p in hdl.buffer_ptrs]
             if len(ptrs) != self.world or ptrs[self.rank] != t.data_ptr():
                 raise RuntimeError("symmetric memory rendezvous returned unexpected buffer pointers")
-            self.buffers.append(t.view(self.world * self.rows, d))
-            self.pointers.append((ctypes.c_void_p * self.world)(*ptrs))
             self._handles.append(hdl)
+            return t, ptrs
+
+        # chunked calls round each chunk's rows per owner up: room for MAX_CHUNKS extra rows per block
+        self.block_rows_total = self.world * (self.rows + self.MAX_CHUNKS)
+        self.buffers, self.buffer_ptrs, self.outs, self.out_ptrs = [], [], [], []
+        for _ in range(buffers):
+            t, ptrs = mapped(self.block_rows_total * d, torch.bfloat16)
+            self.buffers.append(t.view(self.block_rows_total, d))
+            self.buffer_ptrs.append(ptrs)
+            y, yptrs = mapped(max(M, 1) * d, torch.bfloat16)
+            self.outs.append(y.view(max(M, 1), d))
+            self.out_ptrs.append((ctypes.c_void_p * self.world)(*yptrs))
+        self.pointers = [(ctypes.c_void_p * self.world)(*p) for p in self.buffer_ptrs]
+        flags, fptrs = mapped(64, torch.int32)
+        flags.zero_()
+        self._flags = flags
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*fptrs)
+        self._epoch = 0
         self._turn = 0
-        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+        self._side = torch.cuda.Stream(device=device)
+        self._ptr_cache = {}
+        # nobody may signal before every rank's flags are zero
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
 
     def next(self):
+        """(block buffer, its peer pointers, output matrix, its peer pointers) of this call."""
         i = self._turn
         self._turn = (i + 1) % len(self.buffers)
-        return self.buffers[i], self.pointers[i]
+        return i, self.buffers[i], self.pointers[i], self.outs[i], self.out_ptrs[i]
 
-    def barrier(self) -> None:
-        """Stream-ordered barrier: returns (on the stream) once every rank's earlier work on its
-        stream has completed.  A one-element all-reduce: its kernel on each rank starts after that
-        rank's earlier kernels and cannot finish before all ranks have contributed."""
-        dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group)
+    def block_pointers(self, i: int, row_offset: int):
+        """Peer pointers of block buffer ``i`` advanced by ``row_offset`` rows (one chunk's region)."""
+        import ctypes
+        key = (i, row_offset)
+        p = self._ptr_cache.get(key)
+        if p is None:
+            off = row_offset * self.d * 2
+            p = (ctypes.c_void_p * self.world)(*[q + off for q in self.buffer_ptrs[i]])
+            self._ptr_cache[key] = p
+        return p
+
+    def barrier(self, budget_us: int = 0) -> None:
+        """Stream-ordered barrier on the current stream (``ffnk_peer_barrier``): returns, on the stream,
+        once every rank's earlier work on its stream has completed.  Every rank must call the barriers
+        of one ``PeerBlocks`` in the same order.  A rank that never arrives makes the others give up
+        after ``budget_us`` (default 2 s) with a device status code (``check_status`` raises)."""
+        from ._lib import check, lib
+        from .route import status_word, stream_ptr
+        self._epoch += 1
+        check("ffnk_peer_barrier", lib().ffnk_peer_barrier(
+            self._flag_ptrs, self.world, self.rank, self._epoch, budget_us, status_word(self.device).data_ptr(),
+            stream_ptr(self.device)))
 
     def owned_rows(self) -> slice:
         return peer_owned_rows(self.M, self.rank, self.world)
 
 
-def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gather: bool = True):
-    """Tensor-parallel MaskedFFN forward whose down projection writes its partial rows straight
-    into the memory of the rank that owns them (NVLink peer stores from the GEMM epilogue,
-    ``ffnk_ffn_down_to_peers``), followed by one barrier and a local fp32 sum of the ``world``
-    partials (``ffnk_sum_row_blocks``).  The partial ``y`` never exists in this rank's memory and
-    no reduction collective runs.
+def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gather: bool = True, chunks: int = 1):
+    """Tensor-parallel MaskedFFN forward whose communication is done by this library's own kernels
+    over NVLink peer memory; no collective library call is on the path.
 
-    ``gather=True`` returns the full ``y`` on every rank (one all-gather of the owned rows);
-    ``gather=False`` returns ``(rows, y[rows])`` with ``rows = blocks.owned_rows()``.
+    The down projection writes its partial rows straight into the memory of the rank that owns them
+    (peer stores from the GEMM epilogue, ``ffnk_ffn_down_to_peers``: the reduce-scatter's traffic
+    flows while the GEMM computes); after one barrier (``ffnk_peer_barrier``) every owner sums the
+    ``world`` partials in fp32 and stores the bf16 rows into the output of every rank
+    (``ffnk_sum_row_blocks_to_peers``); a second barrier completes the output everywhere.
+
+    ``gather=True`` returns the full ``y`` on every rank: a view of symmetric memory owned by
+    ``blocks``, valid until the call after the next one.  ``gather=False`` returns
+    ``(rows, y[rows])`` with ``rows = blocks.owned_rows()`` and skips the broadcast.
+    ``chunks > 1`` (``gather=True`` only) splits the tokens into that many row ranges; the barrier,
+    sum and broadcast of one chunk run on a side stream under the GEMMs of the next.
     The weights are this rank's shards (``shard_ffn_weights``); ``x`` and ``mask`` are replicated."""
     from ._lib import check, lib
     from .ffn import permute_rows_first
@@ -249,36 +302,93 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
     _check_dims(d=d, h=h)
     if (M, d) != (blocks.M, blocks.d) or x.device != blocks.device:
         raise RuntimeError(f"PeerBlocks were made for [{blocks.M}, {blocks.d}] on {blocks.device}")
+    chunks = max(1, min(int(chunks), blocks.MAX_CHUNKS, max(1, M)))
+    if chunks > 1 and not gather:
+        raise ValueError("chunks > 1 needs gather=True (owned rows are interleaved by chunk)")
     dev = x.device
     L = lib()
-    world, rank, rows = blocks.world, blocks.rank, blocks.rows
+    world, rank = blocks.world, blocks.rank
     with torch.cuda.device(dev):
-        st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
-        own = torch.empty((rows, d), device=dev, dtype=torch.bfloat16)
-        if M > 0:
-            rt = _mask_route(mask, M, dev, None)
+        st = status_word(dev).data_ptr()
+        main = torch.cuda.current_stream(dev)
+        turn, buf, _, y, y_ptrs = blocks.next()
+
+        def compute_chunk(tok: slice, rows_c: int, block_ptrs):
+            """route, (permute,) gate/up and the peer-storing down projection of one token range"""
+            Mc = tok.stop - tok.start
+            sp = stream_ptr(dev)
+            xc, mc = x[tok], mask[tok]
+            rt = _mask_route(mc, Mc, dev, None)
             inter = torch.empty((rt.cap + 512, h), device=dev, dtype=torch.bfloat16)
-            xin, routed_in = x, 0
-            if permute_rows_first(M, d, h):
+            xin, routed_in = xc, 0
+            if permute_rows_first(Mc, d, h):
                 xin = torch.empty((rt.cap + 512, d), device=dev, dtype=torch.bfloat16)
                 check("ffnk_permute_rows", L.ffnk_permute_rows(
-                    x.data_ptr(), x.stride(0), rt.perm.data_ptr(), rt.counts.data_ptr(), xin.data_ptr(),
-                    xin.stride(0), M, d, sp))
+                    xc.data_ptr(), xc.stride(0), rt.perm.data_ptr(), rt.counts.data_ptr(), xin.data_ptr(),
+                    xin.stride(0), Mc, d, sp))
                 routed_in = 1
             check("ffnk_ffn_gateup", L.ffnk_ffn_gateup(
                 xin.data_ptr(), xin.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),
                 w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(),
-                inter.stride(0), routed_in, 1, M, d, h, st, sp))
-            buf, ptrs = blocks.next()
+                inter.stride(0), routed_in, 1, Mc, d, h, st, sp))
             check("ffnk_ffn_down_to_peers", L.ffnk_ffn_down_to_peers(
                 inter.data_ptr(), inter.stride(0), w2.data_ptr(), u2.data_ptr(), w2.stride(0), w2.stride(1),
-                rt.perm.data_ptr(), rt.counts.data_ptr(), ptrs, world, rank, rows, d, M, d, h, st, sp))
+                rt.perm.data_ptr(), rt.counts.data_ptr(), block_ptrs, world, rank, rows_c, d, Mc, d, h, st, sp))
+
+        def sum_chunk(tok: slice, rows_c: int, region_row0: int, to_peers: bool, own=None, max_ctas: int = 0):
+            """this rank's rows of one token range: fp32 sum of the world partials, to every rank or locally"""
+            Mc = tok.stop - tok.start
+            n_own = max(0, min(rows_c, Mc - rank * rows_c))
+            if n_own == 0:
+                return
+            src = buf[region_row0:region_row0 + world * rows_c]
+            sp = stream_ptr(dev)
+            if to_peers:
+                check("ffnk_sum_row_blocks_to_peers", L.ffnk_sum_row_blocks_to_peers(
+                    src.data_ptr(), world, n_own, d, d, y_ptrs, world, tok.start + rank * rows_c, d, max_ctas, sp))
+            else:
+                # blocks are rows_c rows apart; only the first n_own rows of each exist
+                check("ffnk_sum_row_blocks", L.ffnk_sum_row_blocks(src.data_ptr(), world, rows_c, d, d, own.data_ptr(), d, sp))
+
+        if M == 0:
+            if gather:
+                return y[:0]
+            return blocks.owned_rows(), torch.empty((0, d), device=dev, dtype=torch.bfloat16)
+
+        if chunks == 1:
+            tok, rows_c = slice(0, M), blocks.rows
+            compute_chunk(tok, rows_c, blocks.block_pointers(turn, 0))
             blocks.barrier()
-            check("ffnk_sum_row_blocks", L.ffnk_sum_row_blocks(buf.data_ptr(), world, rows, d, d, own.data_ptr(), d, sp))
+            if not gather:
+                own = torch.empty((rows_c, d), device=dev, dtype=torch.bfloat16)
+                sum_chunk(tok, rows_c, 0, False, own)
+                maybe_check(dev)
+                r = blocks.owned_rows()
+                return r, own[: r.stop - r.start]
+            sum_chunk(tok, rows_c, 0, True)
+            blocks.barrier()
+            maybe_check(dev)
+            return y[:M]
+
+        side = blocks._side
+        region = 0
+        for c in range(chunks):
+            tok = row_shard(M, c, chunks)
+            rows_c = peer_block_rows(tok.stop - tok.start, world)
+            compute_chunk(tok, rows_c, blocks.block_pointers(turn, region))
+            ev = torch.cuda.Event()
+            ev.record(main)
+            side.wait_event(ev)
+            with torch.cuda.stream(side):
+                blocks.barrier()
+                # the sum runs beside the next chunk's GEMMs: a quarter of the SMs' worth of CTAs is plenty
+                # for a kernel that is bound by the NVLink, and leaves the GEMM's epilogue warps their issue slots
+                sum_chunk(tok, rows_c, region, True, max_ctas=0 if c == chunks - 1 else 148)
+            region += world * rows_c
+        with torch.cuda.stream(side):
+            blocks.barrier()
+            done = torch.cuda.Event()
+            done.record(side)
+        main.wait_event(done)
         maybe_check(dev)
-        if not gather:
-            r = blocks.owned_rows()
-            return r, own[: r.stop - r.start]
-        y = torch.empty((world * rows, d), device=dev, dtype=torch.bfloat16)
-        dist.all_gather_into_tensor(y, own, group=blocks.group)
         return y[:M]

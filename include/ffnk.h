@@ -192,6 +192,29 @@ int ffnk_sum_row_blocks(const void* blocks, int nblocks, int64_t rows, int64_t d
                         int64_t ldo, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The rest of the tensor-parallel all-reduce with this library's own kernels (no counterpart in the
+ * single-device reference).  After ffnk_ffn_down_to_peers on every rank:
+ *     ffnk_peer_barrier            every rank's partial rows have landed in their owners' buffers
+ *     ffnk_sum_row_blocks_to_peers the owner sums its `nblocks` blocks in fp32 and stores the bf16 rows
+ *                                  into the output matrix of EVERY rank: peer_out[r][(out_row0 + row) * ldo + c]
+ *     ffnk_peer_barrier            every rank's output matrix is complete
+ * flags / peer_out are HOST arrays of `world` device pointers (1 <= world <= 8), entry r belonging to
+ * rank r and mapped into this process like peer_blocks above.  A flag array is int32[8], zeroed once
+ * before its first use.  `epoch` is 1, 2, 3, ... and must be the same on all ranks for the same barrier
+ * (every rank calls the barriers of one flag array in the same order).  The barrier kernel is one warp:
+ * it release-stores `epoch` into slot `rank` of every rank's array, then polls its own array until every
+ * slot has reached `epoch`; after budget_us microseconds (0: the library's 2 s) it gives up, writes a
+ * status code to `status` and returns, so a missing rank surfaces in ffnk_read_status, not as a hang.
+ * Ranks must be separate GPUs (kernels of different ranks waiting for each other on one GPU may never
+ * run at the same time).  max_ctas > 0 caps the grid of the sum (to leave SMs to a concurrent GEMM).
+ * ------------------------------------------------------------------------------------- */
+int ffnk_peer_barrier(void* const* flags, int world, int rank, int32_t epoch, int64_t budget_us, int32_t* status,
+                      void* stream);
+int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int64_t rows, int64_t d, int64_t ldb,
+                                 void* const* peer_out, int world, int64_t out_row0, int64_t ldo, int max_ctas,
+                                 void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Small-M (decode) MaskedFFN forward: streams each present modality's weights once with
  * 128-bit loads; same contract as MaskedFFN.forward (ffn_kernel/ops.py:28-32).
  * inter: scratch bf16 [M, h].  Supported for M <= ffnk_decode_max_tokens() (32) and K-major weights.

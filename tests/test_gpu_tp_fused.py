@@ -40,5 +40,7 @@ def test_two_ranks(M, d, h, mask):
     out = _run(2, "--tokens", str(M), "--dim", str(d), "--hidden", str(h), "--mask-kind", mask)
     assert out["world"] == 2
     assert out["own_rows_equal"]
+    assert out["all_ranks_equal"]
+    assert out["chunked_equal"]
     assert out["fused_vs_oracle"] < TOL
     assert out["fused_vs_nccl"] < TOL

@@ -103,3 +103,58 @@ def test_argument_checks(dev):
     assert L.ffnk_sum_row_blocks(buf.data_ptr(), 2, 32, d + 4, d + 4, buf.data_ptr(), d + 4, sp) < 0
     torch.cuda.synchronize()
     check_status()
+
+
+def test_sum_to_peers_fills_every_ranks_output(dev):
+    """The owner's block sum stored into the output of every rank (here: `world` allocations of one GPU),
+    owner after owner; every output must end up equal to the oracle, rows beyond M untouched."""
+    L = lib()
+    world, M, d, h = 4, 1001, 136, 320
+    c = ffn_case(M, d, h, seed=9, mask=edge_mask(M, "bernoulli", seed=2))
+    ref = O.masked_ffn(*c.apply_args())
+    _, bufs, rows = _emulated_tp_forward(c.to(dev), world, dev)
+    outs = [torch.full((world * rows, d), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    optrs = (ctypes.c_void_p * world)(*[o.data_ptr() for o in outs])
+    sp = stream_ptr(dev)
+    for owner in range(world):
+        n_own = max(0, min(rows, M - owner * rows))
+        assert L.ffnk_sum_row_blocks_to_peers(bufs[owner].data_ptr(), world, n_own, d, d, optrs, world, owner * rows, d,
+                                              0 if owner % 2 else 3, sp) == 0     # also with a capped grid
+    check_status()
+    for o in outs:
+        assert O.max_rel_err(o[:M], ref) < TOL
+        assert torch.equal(o[:M], outs[0][:M])
+        assert torch.isnan(o[M:].float()).all()
+    assert L.ffnk_sum_row_blocks_to_peers(bufs[0].data_ptr(), 9, rows, d, d, optrs, world, 0, d, 0, sp) < 0
+    assert L.ffnk_sum_row_blocks_to_peers(bufs[0].data_ptr(), world, rows, d, d, optrs, 0, 0, d, 0, sp) < 0
+
+
+def test_peer_barrier_alone_and_with_a_missing_rank(dev):
+    """One rank: the barrier passes on its own flag.  Two ranks of which one never arrives (its flag is
+    simply never written): the wait gives up after its budget, reports a status code, and the
+    context stays usable.  An arrival written by the host beforehand lets the wait pass."""
+    from ffn_kernel_b200._lib import FfnkError
+    L = lib()
+    st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
+    mine = torch.zeros(8, dtype=torch.int32, device=dev)
+    other = torch.zeros(8, dtype=torch.int32, device=dev)
+    one = (ctypes.c_void_p * 1)(mine.data_ptr())
+    for epoch in (1, 2, 3):
+        assert L.ffnk_peer_barrier(one, 1, 0, epoch, 0, st, sp) == 0
+    check_status()
+    assert mine[0].item() == 3
+    two = (ctypes.c_void_p * 2)(mine.data_ptr(), other.data_ptr())
+    mine.zero_()
+    mine[1] = 5                                    # "rank 1 has reached barrier 5 already"
+    assert L.ffnk_peer_barrier(two, 2, 0, 5, 1000, st, sp) == 0
+    check_status()
+    assert other[0].item() == 5                    # and rank 1 was told that rank 0 arrived
+    assert L.ffnk_peer_barrier(two, 2, 0, 6, 1000, st, sp) == 0     # nobody writes mine[1] = 6: 1 ms budget
+    with pytest.raises(FfnkError) as err:
+        check_status()
+    assert "rank" in str(err.value)
+    check_status()                                  # the status word was cleared, the device still works
+    assert (torch.ones(4, device=dev) * 2).sum().item() == 8
+    assert L.ffnk_peer_barrier(two, 9, 0, 1, 0, st, sp) < 0      # more than eight ranks
+    assert L.ffnk_peer_barrier(two, 2, 2, 1, 0, st, sp) < 0      # rank outside the world
+    assert L.ffnk_peer_barrier(None, 1, 0, 1, 0, st, sp) < 0

@@ -1,7 +1,8 @@
 """One rank of the multi-GPU check of ``masked_ffn_tp_fused`` (run under torch.distributed.run by
 ``test_gpu_tp_fused.py``; not collected by pytest).  Every rank computes the tensor-parallel
-MaskedFFN three ways -- fused peer stores with and without the final all-gather, and partial
-outputs summed by an NCCL all-reduce -- and rank 0 compares them with the fp32 oracle.  With
+MaskedFFN several ways -- fused peer stores with the result broadcast to every rank (whole and in
+token chunks) or left row-sharded, and partial outputs summed by an NCCL all-reduce -- and rank 0
+compares them with the fp32 oracle.  With
 ``--time`` it also prints device timings of the variants."""
 import argparse
 import json
@@ -57,12 +58,23 @@ def main():
     out = {}
     for rep in range(3):                       # repeated calls alternate the two block buffers
         y_fused = tp.masked_ffn_tp_fused(x, *shards, mask, blocks)
+    y_fused = y_fused.clone()                  # the result lives in the group's buffers (valid for two calls)
     rows, y_own = tp.masked_ffn_tp_fused(x, *shards, mask, blocks, gather=False)
     y_nccl = tp.masked_ffn_tp(x, *shards, mask)
+    y_chunked = {c: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, chunks=c).clone() for c in (2, 3)}
     torch.cuda.synchronize()
     check_status()
     out["fused_vs_nccl"] = float((y_fused.float() - y_nccl.float()).abs().max() / y_nccl.float().abs().max())
     out["own_rows_equal"] = bool(torch.equal(y_own, y_fused[rows]))
+    # a chunk routes its own token range, so tile boundaries differ from the unchunked call; the sums
+    # are the same fp32 sums of the same bf16 partials, hence bit-identical rows
+    out["chunked_equal"] = all(bool(torch.equal(v, y_fused)) for v in y_chunked.values())
+    # every rank must hold the same full result
+    ref_y = y_fused.clone()
+    dist.broadcast(ref_y, 0)
+    same_y = torch.tensor([1.0 if torch.equal(ref_y, y_fused) else 0.0], device=dev)
+    dist.all_reduce(same_y, op=dist.ReduceOp.MIN)
+    out["all_ranks_equal"] = bool(same_y.item() == 1.0)
     same = torch.tensor([1.0 if out["own_rows_equal"] else 0.0], device=dev)
     dist.all_reduce(same, op=dist.ReduceOp.MIN)
     out["own_rows_equal"] = bool(same.item() == 1.0)
@@ -73,7 +85,9 @@ def main():
         out["nccl_vs_oracle"] = float(O.max_rel_err(y_nccl, ref))
     if args.time:
         flops = 6.0 * args.tokens * args.dim * args.hidden
-        for name, fn in (("fused_allgather", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks)),
+        for name, fn in (("fused_broadcast", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks)),
+                         ("fused_broadcast_2chunks", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, chunks=2)),
+                         ("fused_broadcast_4chunks", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, chunks=4)),
                          ("fused_row_sharded", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, gather=False)),
                          ("nccl_all_reduce", lambda: tp.masked_ffn_tp(x, *shards, mask)),
                          ("nccl_reduce_scatter", (lambda: tp.masked_ffn_tp_reduce_scatter(x, *shards, mask))
