@@ -27,6 +27,9 @@ SIGNATURES = {
     "ffnk_linear_bwd": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                 c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ffnk_linear_bwd_parts": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                      c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "ffnk_permute_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                   c_void_p]),
     "ffnk_ffn_gateup": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
@@ -39,8 +42,8 @@ SIGNATURES = {
                                        c_void_p, c_void_p]),
     "ffnk_sum_row_blocks": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
     "ffnk_peer_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_int32, c_int64, c_void_p, c_void_p]),
-    "ffnk_sum_row_blocks_to_peers": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, POINTER(c_void_p), c_int,
-                                             c_int64, c_int64, c_int, c_void_p]),
+    "ffnk_sum_row_blocks_to_peers": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, POINTER(c_void_p),
+                                             c_int, c_int64, c_int64, c_int, c_void_p]),
     "ffnk_decode_max_tokens": (c_int, []),
     "ffnk_ffn_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,

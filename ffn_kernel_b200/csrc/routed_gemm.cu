@@ -1892,10 +1892,15 @@ extern "C" int ffnk_ffn_down_to_peers(const void* inter, int64_t ldi, const void
   return launch_gemm<A_ROUTED, EPI_STORE, OUT_PEER>(tmA, tmB, mn1, p, M, tile, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
-                               int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm, const int32_t* counts,
-                               void* da, int64_t ldda, void* db1, void* db2, void* g_copy, void* a_copy, int64_t M,
-                               int64_t N, int64_t K, int32_t* status, void* stream) {
+// parts: 1 = the routed-order copies of g and a, 2 = the weight gradients, 4 = dx; ffnk_linear_bwd runs
+// copies, dx, weight gradients.  A data-parallel caller runs 1|2 first, starts the all-reduce of the weight
+// gradients on another stream, and then runs 4 beside it.
+extern "C" int ffnk_linear_bwd_parts(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1,
+                                     const void* b2, int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm,
+                                     const int32_t* counts, void* da, int64_t ldda, void* db1, void* db2, void* g_copy,
+                                     void* a_copy, int64_t M, int64_t N, int64_t K, int parts, int32_t* status,
+                                     void* stream) {
+  if (parts < 1 || parts > 7) return FFNK_ERR_SHAPE;
   if (!db1 || !db2) return FFNK_ERR_NULL;
   if (bad_dim(N) || bad_dim(K) || M < 0 || M >= (1ll << 30)) return FFNK_ERR_SHAPE;
   const bool k_major = (b_stride_k == 1 && b_stride_n >= K);   // storage [N, K]
@@ -1928,14 +1933,17 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
   const bool copies = g_copy && a_copy;
   const int64_t copy_rows = ffnk_route_capacity(M) + 512;
   if (copies && ((reinterpret_cast<uintptr_t>(g_copy) | reinterpret_cast<uintptr_t>(a_copy)) & 15)) return FFNK_ERR_ALIGN;
+  if (copies && (parts & 1)) {
+    int r;
+    if ((r = permute_rows_launch(g, ldg, perm, counts, g_copy, N, M, N, 0, stream))) return r;
+    if (a && (r = permute_rows_launch(a, lda, perm, counts, a_copy, K, M, K, 0, stream))) return r;
+  }
   // dx: the forward kernel on g with the weights seen as [N, K] (contraction over N)
-  {
+  if (parts & 4) {
     AMaps tmA;
     CUtensorMap tmB[4];
     int r;
     if (copies) {
-      if ((r = permute_rows_launch(g, ldg, perm, counts, g_copy, N, M, N, 0, stream))) return r;
-      if (a && (r = permute_rows_launch(a, lda, perm, counts, a_copy, K, M, K, 0, stream))) return r;
       if ((r = make_tensor_map_2d(&tmA.m[RUN_LEVELS], g_copy, N, copy_rows, N, BK, BM))) return r;
       for (int i = 0; i <= COPY_MAP; ++i)
         if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
@@ -1956,7 +1964,7 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     if (r) return r;
   }
   // dW: output in the weight's storage order; P supplies the storage rows, Q the storage columns
-  {
+  if (parts & 2) {
     const void* gg = copies ? g_copy : g;
     const void* aa = copies ? a_copy : a;
     const int64_t lg = copies ? N : ldg, la = copies ? K : lda;
@@ -1967,6 +1975,15 @@ extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_
     return launch_wgrad(P, ldp, p_dim, Q, ldq, q_dim, copies ? copy_rows : M, db1, db2,
                         k_major ? b_stride_n : b_stride_k, copies ? 1 : 0, perm, counts, status, s);
   }
+  return 0;
+}
+
+extern "C" int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
+                               int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm, const int32_t* counts,
+                               void* da, int64_t ldda, void* db1, void* db2, void* g_copy, void* a_copy, int64_t M,
+                               int64_t N, int64_t K, int32_t* status, void* stream) {
+  return ffnk_linear_bwd_parts(g, ldg, a, lda, b1, b2, b_stride_k, b_stride_n, perm, counts, da, ldda, db1, db2, g_copy,
+                               a_copy, M, N, K, 7, status, stream);
 }
 
 // -------------------------------------------------------------------------------------------

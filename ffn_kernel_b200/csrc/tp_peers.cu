@@ -119,12 +119,13 @@ extern "C" int ffnk_peer_barrier(void* const* flags, int world, int rank, int32_
   return cuda_status(cudaGetLastError());
 }
 
-extern "C" int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int64_t rows, int64_t d, int64_t ldb,
-                                            void* const* peer_out, int world, int64_t out_row0, int64_t ldo,
-                                            int max_ctas, void* stream) {
+extern "C" int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int64_t block_rows, int64_t rows, int64_t d,
+                                            int64_t ldb, void* const* peer_out, int world, int64_t out_row0,
+                                            int64_t ldo, int max_ctas, void* stream) {
   if (rows == 0) return 0;
   if (!blocks || !peer_out) return FFNK_ERR_NULL;
-  if (nblocks < 1 || nblocks > kMaxPeers || world < 1 || world > kMaxPeers || rows < 0 || rows >= (1ll << 30) ||
+  if (nblocks < 1 || nblocks > kMaxPeers || world < 1 || world > kMaxPeers || rows < 0 || rows > block_rows ||
+      block_rows >= (1ll << 30) ||
       out_row0 < 0 || out_row0 >= (1ll << 30) || d < 8 || (d & 7) || d >= (1ll << 30) || max_ctas < 0)
     return FFNK_ERR_SHAPE;
   if ((ldb & 7) || (ldo & 7) || ldb < d || ldo < d || (reinterpret_cast<uintptr_t>(blocks) & 15)) return FFNK_ERR_ALIGN;
@@ -140,7 +141,7 @@ extern "C" int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int
   const int64_t max_grid = max_ctas > 0 ? max_ctas : static_cast<int64_t>(dev.sm_count) * 8;
   if (grid > max_grid) grid = max_grid;
   sum_blocks_to_peers_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(blocks), nblocks, rows * (ldb / 8), ldb / 8, rows, static_cast<int>(d / 8), out, world,
+      static_cast<const uint4*>(blocks), nblocks, block_rows * (ldb / 8), ldb / 8, rows, static_cast<int>(d / 8), out, world,
       out_row0, ldo / 8);
   return cuda_status(cudaGetLastError());
 }

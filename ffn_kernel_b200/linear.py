@@ -149,6 +149,13 @@ def _bf16_linear_train_forward(a, b1, b2, mask, rt: Route | None = None):
     return c, a_routed
 
 
+# Data-parallel training: when set (``tp.GradientSync`` does), ``_bf16_linear_backward`` computes the
+# weight gradients first, calls ``GRAD_HOOK(db1, db2)`` -- which starts their all-reduce on another
+# stream and returns a function -- launches the dx GEMM beside it, and calls the returned function,
+# which makes the launching stream wait for the reduced gradients.  None in normal use.
+GRAD_HOOK = None
+
+
 def _bf16_linear_backward(gd, a, b1, b2, mask, rt: Route | None = None, a_routed=None):
     """Returns (da, db1, db2); db1/db2 carry the strides of b1/b2 (``empty_like``,
     ``ffn_kernel/linear.py:475``).  ``a_routed``: the routed-order copy of ``a`` a training forward
@@ -181,10 +188,18 @@ def _bf16_linear_backward(gd, a, b1, b2, mask, rt: Route | None = None, a_routed
         else:
             g_copy, a_copy = _copy_scratch(M, N, dev), _copy_scratch(M, K, dev)
             a_ptr, a_ld = a.data_ptr(), a.stride(0)
-        check("ffnk_linear_bwd", lib().ffnk_linear_bwd(
-            gd.data_ptr(), gd.stride(0), a_ptr, a_ld, b1.data_ptr(), b2.data_ptr(),
-            b1.stride(0), b1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(),
-            da.data_ptr(), da.stride(0), db1.data_ptr(), db2.data_ptr(), _ptr(g_copy), _ptr(a_copy), M, N, K,
-            status_word(dev).data_ptr(), stream_ptr(dev)))
+        args = (gd.data_ptr(), gd.stride(0), a_ptr, a_ld, b1.data_ptr(), b2.data_ptr(),
+                b1.stride(0), b1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(),
+                da.data_ptr(), da.stride(0), db1.data_ptr(), db2.data_ptr(), _ptr(g_copy), _ptr(a_copy), M, N, K)
+        tail = (status_word(dev).data_ptr(), stream_ptr(dev))
+        if GRAD_HOOK is None:
+            check("ffnk_linear_bwd", lib().ffnk_linear_bwd(*args, *tail))
+        else:
+            check("ffnk_linear_bwd_parts", lib().ffnk_linear_bwd_parts(*args, 1 | 2, *tail))
+            finish = GRAD_HOOK(db1, db2)
+            try:
+                check("ffnk_linear_bwd_parts", lib().ffnk_linear_bwd_parts(*args, 4, *tail))
+            finally:
+                finish()
     maybe_check(dev)
     return da, db1, db2

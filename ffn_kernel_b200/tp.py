@@ -154,6 +154,68 @@ def all_reduce_gradients(tensors: Sequence[torch.Tensor], group=None, bucket_byt
     flush()
 
 
+class GradientSync:
+    """Data-parallel training: all-reduce the weight gradients of every ``MaskedLinear`` backward inside
+    the ``with`` block while that backward's dx GEMM runs.
+
+    The backward computes the weight gradients first; the hook packs them into one fp32 bucket and starts
+    the NCCL all-reduce on a side stream; the dx GEMM is launched on the compute stream beside it, leaving
+    ``sm_margin`` SMs to the collective's kernels; before the backward returns, the compute stream is made
+    to wait for the reduced gradients (written back in place), so autograd only ever sees the sums.  What
+    the dx GEMM does not cover of the all-reduce is exposed.  The reference has no distributed path
+    (``ffn_kernel/linear.py:455-496`` is the single-device partial)."""
+
+    def __init__(self, group=None, average: bool = False, sm_margin: int = 16, reduce_dtype=torch.float32):
+        self.group, self.average, self.sm_margin, self.reduce_dtype = group, average, sm_margin, reduce_dtype
+        self._stream = None
+        self._prev = None
+
+    def __enter__(self):
+        from . import linear
+        self._prev = linear.GRAD_HOOK
+        linear.GRAD_HOOK = self._hook
+        return self
+
+    def __exit__(self, *exc):
+        from . import linear
+        linear.GRAD_HOOK = self._prev
+        return False
+
+    def _hook(self, *grads):
+        if not dist.is_initialized() or dist.get_world_size(self.group) == 1:
+            return lambda: None
+        from ._lib import lib
+        dev = grads[0].device
+        if self._stream is None or self._stream.device != dev:
+            self._stream = torch.cuda.Stream(device=dev)
+        main = torch.cuda.current_stream(dev)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        side = self._stream
+        side.wait_event(ready)
+        world = dist.get_world_size(self.group)
+        with torch.cuda.stream(side):
+            flat = torch.cat([g.reshape(-1).to(self.reduce_dtype) for g in grads])
+            work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            work.wait()                                 # stream-level: the side stream waits, the host does not
+            if self.average:
+                flat /= world
+            off = 0
+            for g in grads:
+                n = g.numel()
+                g.copy_(flat[off:off + n].view(g.shape))   # honours the (possibly transposed) strides
+                off += n
+            done = torch.cuda.Event()
+            done.record(side)
+        lib().ffnk_set_sm_margin(self.sm_margin)        # the dx GEMM launched next leaves SMs to the collective
+
+        def finish(flat=flat, grads=grads):
+            lib().ffnk_set_sm_margin(0)
+            main.wait_event(done)
+            flat.record_stream(main)
+        return finish
+
+
 def peer_block_rows(M: int, world: int) -> int:
     """Rows per owner in the fused tensor-parallel path: token ``t`` belongs to rank ``t // rows``."""
     if world < 1:
@@ -290,7 +352,7 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
     sum and broadcast of one chunk run on a side stream under the GEMMs of the next.
     The weights are this rank's shards (``shard_ffn_weights``); ``x`` and ``mask`` are replicated."""
     from ._lib import check, lib
-    from .ffn import permute_rows_first
+    from .ffn import _phase, permute_rows_first
     from .linear import _activation, _check_dims, _mask_route, _weights
     from .route import maybe_check, status_word, stream_ptr
 
@@ -318,22 +380,27 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
             Mc = tok.stop - tok.start
             sp = stream_ptr(dev)
             xc, mc = x[tok], mask[tok]
+            _phase("route")
             rt = _mask_route(mc, Mc, dev, None)
             inter = torch.empty((rt.cap + 512, h), device=dev, dtype=torch.bfloat16)
             xin, routed_in = xc, 0
             if permute_rows_first(Mc, d, h):
+                _phase("permute")
                 xin = torch.empty((rt.cap + 512, d), device=dev, dtype=torch.bfloat16)
                 check("ffnk_permute_rows", L.ffnk_permute_rows(
                     xc.data_ptr(), xc.stride(0), rt.perm.data_ptr(), rt.counts.data_ptr(), xin.data_ptr(),
                     xin.stride(0), Mc, d, sp))
                 routed_in = 1
+            _phase("gateup")
             check("ffnk_ffn_gateup", L.ffnk_ffn_gateup(
                 xin.data_ptr(), xin.stride(0), w1.data_ptr(), w3.data_ptr(), u1.data_ptr(), u3.data_ptr(),
                 w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(),
                 inter.stride(0), routed_in, 1, Mc, d, h, st, sp))
+            _phase("down")
             check("ffnk_ffn_down_to_peers", L.ffnk_ffn_down_to_peers(
                 inter.data_ptr(), inter.stride(0), w2.data_ptr(), u2.data_ptr(), w2.stride(0), w2.stride(1),
                 rt.perm.data_ptr(), rt.counts.data_ptr(), block_ptrs, world, rank, rows_c, d, Mc, d, h, st, sp))
+            _phase("end")
 
         def sum_chunk(tok: slice, rows_c: int, region_row0: int, to_peers: bool, own=None, max_ctas: int = 0):
             """this rank's rows of one token range: fp32 sum of the world partials, to every rank or locally"""
@@ -345,7 +412,7 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
             sp = stream_ptr(dev)
             if to_peers:
                 check("ffnk_sum_row_blocks_to_peers", L.ffnk_sum_row_blocks_to_peers(
-                    src.data_ptr(), world, n_own, d, d, y_ptrs, world, tok.start + rank * rows_c, d, max_ctas, sp))
+                    src.data_ptr(), world, rows_c, n_own, d, d, y_ptrs, world, tok.start + rank * rows_c, d, max_ctas, sp))
             else:
                 # blocks are rows_c rows apart; only the first n_own rows of each exist
                 check("ffnk_sum_row_blocks", L.ffnk_sum_row_blocks(src.data_ptr(), world, rows_c, d, d, own.data_ptr(), d, sp))

@@ -123,6 +123,15 @@ int ffnk_linear_bwd(const void* g, int64_t ldg, const void* a, int64_t lda, cons
                     int64_t ldda, void* db1, void* db2, void* g_copy, void* a_copy, int64_t M, int64_t N, int64_t K,
                     int32_t* status, void* stream);
 
+/* The same in separately callable parts, for data-parallel training (no counterpart in the single-device
+ * reference): parts is a bit mask, 1 = the routed-order copies of g and a, 2 = the weight gradients,
+ * 4 = dx.  ffnk_linear_bwd is parts = 7.  A caller that sums weight gradients over ranks runs 1|2,
+ * starts the all-reduce of db1/db2 on another stream, and runs 4 on this stream beside it. */
+int ffnk_linear_bwd_parts(const void* g, int64_t ldg, const void* a, int64_t lda, const void* b1, const void* b2,
+                          int64_t b_stride_k, int64_t b_stride_n, const int32_t* perm, const int32_t* counts, void* da,
+                          int64_t ldda, void* db1, void* db2, void* g_copy, void* a_copy, int64_t M, int64_t N,
+                          int64_t K, int parts, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Copies the rows of x [M, d] into routed order: out [(cap + 512), d], visual rows first, text
  * rows from row 256 * ceil(Mv / 256).  No counterpart in the reference (it never reorders
@@ -195,8 +204,9 @@ int ffnk_sum_row_blocks(const void* blocks, int nblocks, int64_t rows, int64_t d
  * The rest of the tensor-parallel all-reduce with this library's own kernels (no counterpart in the
  * single-device reference).  After ffnk_ffn_down_to_peers on every rank:
  *     ffnk_peer_barrier            every rank's partial rows have landed in their owners' buffers
- *     ffnk_sum_row_blocks_to_peers the owner sums its `nblocks` blocks in fp32 and stores the bf16 rows
- *                                  into the output matrix of EVERY rank: peer_out[r][(out_row0 + row) * ldo + c]
+ *     ffnk_sum_row_blocks_to_peers the owner sums its `nblocks` blocks (block_rows rows apart; the first
+ *                                  `rows` <= block_rows rows of each) in fp32 and stores the bf16 rows into
+ *                                  the output matrix of EVERY rank: peer_out[r][(out_row0 + row) * ldo + c]
  *     ffnk_peer_barrier            every rank's output matrix is complete
  * flags / peer_out are HOST arrays of `world` device pointers (1 <= world <= 8), entry r belonging to
  * rank r and mapped into this process like peer_blocks above.  A flag array is int32[8], zeroed once
@@ -210,9 +220,9 @@ int ffnk_sum_row_blocks(const void* blocks, int nblocks, int64_t rows, int64_t d
  * ------------------------------------------------------------------------------------- */
 int ffnk_peer_barrier(void* const* flags, int world, int rank, int32_t epoch, int64_t budget_us, int32_t* status,
                       void* stream);
-int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int64_t rows, int64_t d, int64_t ldb,
-                                 void* const* peer_out, int world, int64_t out_row0, int64_t ldo, int max_ctas,
-                                 void* stream);
+int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int64_t block_rows, int64_t rows, int64_t d,
+                                 int64_t ldb, void* const* peer_out, int world, int64_t out_row0, int64_t ldo,
+                                 int max_ctas, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Small-M (decode) MaskedFFN forward: streams each present modality's weights once with

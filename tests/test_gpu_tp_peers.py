@@ -118,15 +118,16 @@ def test_sum_to_peers_fills_every_ranks_output(dev):
     sp = stream_ptr(dev)
     for owner in range(world):
         n_own = max(0, min(rows, M - owner * rows))
-        assert L.ffnk_sum_row_blocks_to_peers(bufs[owner].data_ptr(), world, n_own, d, d, optrs, world, owner * rows, d,
-                                              0 if owner % 2 else 3, sp) == 0     # also with a capped grid
+        assert L.ffnk_sum_row_blocks_to_peers(bufs[owner].data_ptr(), world, rows, n_own, d, d, optrs, world,
+                                              owner * rows, d, 0 if owner % 2 else 3, sp) == 0     # also with a capped grid
     check_status()
     for o in outs:
         assert O.max_rel_err(o[:M], ref) < TOL
         assert torch.equal(o[:M], outs[0][:M])
         assert torch.isnan(o[M:].float()).all()
-    assert L.ffnk_sum_row_blocks_to_peers(bufs[0].data_ptr(), 9, rows, d, d, optrs, world, 0, d, 0, sp) < 0
-    assert L.ffnk_sum_row_blocks_to_peers(bufs[0].data_ptr(), world, rows, d, d, optrs, 0, 0, d, 0, sp) < 0
+    assert L.ffnk_sum_row_blocks_to_peers(bufs[0].data_ptr(), 9, rows, rows, d, d, optrs, world, 0, d, 0, sp) < 0
+    assert L.ffnk_sum_row_blocks_to_peers(bufs[0].data_ptr(), world, rows, rows, d, d, optrs, 0, 0, d, 0, sp) < 0
+    assert L.ffnk_sum_row_blocks_to_peers(bufs[0].data_ptr(), world, rows, rows + 1, d, d, optrs, world, 0, d, 0, sp) < 0
 
 
 def test_peer_barrier_alone_and_with_a_missing_rank(dev):
