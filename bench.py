@@ -858,7 +858,6 @@ def c3_token_sharded(b: Bench) -> dict:
         xs.grad = wv.grad = wt.grad = None
         with sync:
             MaskedLinear.apply(xs, wv.T, wt.T, ms_).backward(gs)
-        sync.wait()
     out["with_overlapped_grad_allreduce_ms"] = b.time_steps(step_overlapped, n, 3)
     out["allreduce_exposed_ms"] = out["with_overlapped_grad_allreduce_ms"] - ms
     out["allreduce_hidden_ms"] = out["with_grad_allreduce_ms"] - out["with_overlapped_grad_allreduce_ms"]

@@ -154,6 +154,14 @@ def all_reduce_gradients(tensors: Sequence[torch.Tensor], group=None, bucket_byt
     flush()
 
 
+def _storage_order_view(t: torch.Tensor) -> torch.Tensor:
+    """A view of ``t`` whose logical order is its memory order when ``t`` is a transposed dense matrix
+    (so that flattening it is free); ``t`` itself otherwise."""
+    if t.dim() == 2 and not t.is_contiguous() and t.T.is_contiguous():
+        return t.T
+    return t
+
+
 class GradientSync:
     """Data-parallel training: all-reduce the weight gradients of every ``MaskedLinear`` backward inside
     the ``with`` block while that backward's dx GEMM runs.
@@ -195,15 +203,18 @@ class GradientSync:
         side.wait_event(ready)
         world = dist.get_world_size(self.group)
         with torch.cuda.stream(side):
-            flat = torch.cat([g.reshape(-1).to(self.reduce_dtype) for g in grads])
+            # gradients are packed in the order of their storage (a weight gradient carries its weight's
+            # strides, usually the transposed view of [out, in] storage): a flat view, not a transposing copy
+            views = [_storage_order_view(g) for g in grads]
+            flat = torch.cat([v.reshape(-1).to(self.reduce_dtype) for v in views])
             work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
             work.wait()                                 # stream-level: the side stream waits, the host does not
             if self.average:
                 flat /= world
             off = 0
-            for g in grads:
-                n = g.numel()
-                g.copy_(flat[off:off + n].view(g.shape))   # honours the (possibly transposed) strides
+            for v in views:
+                n = v.numel()
+                v.copy_(flat[off:off + n].view(v.shape))
                 off += n
             done = torch.cuda.Event()
             done.record(side)
