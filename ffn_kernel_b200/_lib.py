@@ -48,6 +48,10 @@ SIGNATURES = {
     "ffnk_ffn_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ffnk_ffn_small_max_tokens": (c_int, []),
+    "ffnk_ffn_small": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
+                               c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "ffnk_ffn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "ffnk_ffn_permute_first": (c_int, [c_int64, c_int64, c_int64]),
     "ffnk_ffn_forward": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -61,6 +65,7 @@ SIGNATURES = {
     "ffnk_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
     "ffnk_set_sm_margin": (c_int, [c_int]),
     "ffnk_debug_profile_buffer": (c_int, [c_void_p]),
+    "ffnk_tune_override": (c_int, [c_char_p, c_int]),
     "ffnk_status_string": (c_char_p, [c_int]),
 }
 
@@ -89,7 +94,28 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)      # AttributeError if the library lacks a declared symbol
             fn.restype, fn.argtypes = res, args
         _lib = handle
+        _apply_env_overrides(handle)
     return _lib
+
+
+# Tile-table overrides for measurements (`python -m ffn_kernel_b200.tune`, the forced-variant test runs):
+# FFNK_PAIR, FFNK_NARROW, FFNK_PERMUTE, FFNK_EPI_WARPS, FFNK_GROUP_M, FFNK_WGRAD_PAIR, FFNK_MAX_RUN_ROWS,
+# FFNK_COPY_THRESHOLD, FFNK_VERBOSE are read HERE, once, and handed to the library through
+# ffnk_tune_override; the library itself never looks at the environment.
+_ENV_OVERRIDES = ("pair", "narrow", "permute", "epi_warps", "group_m", "wgrad_pair", "max_run_rows",
+                  "copy_threshold", "verbose")
+
+
+def _apply_env_overrides(handle) -> None:
+    for name in _ENV_OVERRIDES:
+        raw = os.environ.get("FFNK_" + name.upper())
+        if raw is None or raw == "":
+            continue
+        try:
+            value = int(raw)
+        except ValueError:
+            raise RuntimeError(f"FFNK_{name.upper()}={raw!r} is not an integer") from None
+        check(f"ffnk_tune_override({name})", handle.ffnk_tune_override(name.encode(), value))
 
 
 def check(where: str, code: int) -> None:

@@ -1,7 +1,7 @@
 // Host utilities of libffnk: device query, tensor-map construction, status word access,
 // and the bounded-wait self test.
 #include <cstdio>
-#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "ffnk_internal.h"
@@ -23,6 +23,11 @@ const DeviceInfo& device_info() {
     cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   }
   return d;
+}
+
+TuneOverrides& tune_overrides() {
+  static TuneOverrides t;
+  return t;
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -66,7 +71,7 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint6
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS && getenv("FFNK_VERBOSE"))
+  if (r != CUDA_SUCCESS && tune_overrides().verbose > 0)
     fprintf(stderr, "ffnk: cuTensorMapEncodeTiled failed (CUresult %d): base %p dims {%llu, %llu} row stride %llu B box {%u, %u}\n",
             static_cast<int>(r), base, static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
             static_cast<unsigned long long>(row_stride * 2), box_inner, box_outer);
@@ -118,6 +123,21 @@ extern "C" int ffnk_selftest_bounded_wait(int32_t* status, int64_t budget_us, vo
   return cuda_status(cudaGetLastError());
 }
 
+extern "C" int ffnk_tune_override(const char* name, int value) {
+  if (!name) return FFNK_ERR_NULL;
+  TuneOverrides& t = tune_overrides();
+  struct { const char* n; int* v; } table[] = {
+      {"pair", &t.pair}, {"narrow", &t.narrow}, {"permute", &t.permute}, {"epi_warps", &t.epi_warps},
+      {"group_m", &t.group_m}, {"wgrad_pair", &t.wgrad_pair}, {"max_run_rows", &t.max_run_rows},
+      {"copy_threshold", &t.copy_threshold}, {"verbose", &t.verbose}};
+  for (auto& e : table)
+    if (strcmp(e.n, name) == 0) {
+      *e.v = value;
+      return 0;
+    }
+  return FFNK_ERR_SHAPE;
+}
+
 extern "C" const char* ffnk_status_string(int code) {
   switch (code) {
     case 0: return "ok";
@@ -138,6 +158,7 @@ extern "C" const char* ffnk_status_string(int code) {
     case ST_TIMEOUT_TEST: return "device: self-test wait expired (expected)";
     case ST_TIMEOUT_PEER: return "device: wait on partner CTA expired";
     case ST_TIMEOUT_RANK: return "device: barrier wait for another rank expired";
+    case ST_TIMEOUT_GRID: return "device: grid-wide wait of the small-M forward expired";
     default: return code <= -1000 ? "CUDA runtime error, code = -(1000 + cudaError_t)" : "unknown code";
   }
 }

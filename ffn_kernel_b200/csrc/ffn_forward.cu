@@ -3,8 +3,6 @@
 // weight-streaming decode pair for a handful of tokens.  Same contract as MaskedFFN.forward
 // (ffn_kernel/ops.py:28-32).  One call keeps the host cost of a forward pass at a few
 // microseconds, which is what matters when the kernels themselves take ten.
-#include <cstdlib>
-
 #include "ffnk_internal.h"
 
 namespace ffnk {
@@ -19,10 +17,7 @@ static int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 // M=16384, d=4096, h=1376: forward 0.499 ms gathering, 0.466 ms copying first).
 static bool permute_first(int64_t M, int64_t d, int64_t h) {
   (void)d;
-  static const int forced = [] {
-    const char* e = getenv("FFNK_PERMUTE");
-    return e ? atoi(e) : -1;
-  }();
+  const int forced = tune_overrides().permute;
   if (forced >= 0) return forced != 0;
   return M < 2048 || h >= 1280;
 }

@@ -30,6 +30,22 @@ const DeviceInfo& device_info();
 int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride,
                        uint32_t box_inner, uint32_t box_outer);
 
+// Overrides of single tile-table entries, for measuring a choice against its alternatives
+// (ffnk_tune_override; `python -m ffn_kernel_b200.tune`).  -1 = the table decides.  The library reads
+// no environment variables: whoever wants an override sets it through the C ABI.
+struct TuneOverrides {
+  int pair = -1;            // 0/1: CTA pairs never / wherever the kernel variant exists
+  int narrow = -1;          // 0: 256-column tiles only, 1: 64-column, 2: 128-column tiles
+  int permute = -1;         // 0/1: FFN forward gathers rows in the gate/up GEMM / copies x to routed order first
+  int epi_warps = -1;       // 4 or 8 epilogue warps
+  int group_m = -1;         // row tiles per super-tile
+  int wgrad_pair = -1;      // 0/1: weight gradients on single CTAs / CTA pairs
+  int max_run_rows = -1;    // largest tiled TMA box for runs of consecutive tokens (0: gather4 only)
+  int copy_threshold = -1;  // average run length below which MaskedLinear forward copies a to routed order
+  int verbose = -1;         // 1: print the arguments of a tensor map the driver rejects
+};
+TuneOverrides& tune_overrides();
+
 // permute_rows with an optional device-side gate: with only_if_scattered = T > 0 the kernel returns at
 // once unless the mask's runs of same-modality tokens average fewer than T rows.
 int permute_rows_launch(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out, int64_t ldo,

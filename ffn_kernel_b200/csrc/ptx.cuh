@@ -24,6 +24,7 @@ enum : int {
   ST_TIMEOUT_TEST = 6,       // the self-test wait (a barrier nobody arrives on) expired, as designed
   ST_TIMEOUT_PEER = 7,       // wait on the partner CTA of a pair expired
   ST_TIMEOUT_RANK = 8,       // barrier between tensor-parallel ranks: another rank's flag never arrived
+  ST_TIMEOUT_GRID = 9,       // grid-wide wait between the phases of the small-M forward expired
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -26,8 +26,6 @@
 // under the main loop of tile i+1.
 #include <cuda_bf16.h>
 
-#include <cstdlib>
-
 #include "ffnk_internal.h"
 #include "ptx.cuh"
 
@@ -48,10 +46,7 @@ constexpr int GEMM_THREADS_MAX = 320;
 constexpr int GEMM_THREADS = 192;
 __device__ __forceinline__ int epilogue_parts() { return (static_cast<int>(blockDim.x) - 64) >> 7; }
 static int gemm_threads_for(int64_t k_len_total) {
-  static const int forced = [] {   // FFNK_EPI_WARPS=4/8 overrides the choice for experiments
-    const char* e = getenv("FFNK_EPI_WARPS");
-    return e ? atoi(e) : 0;
-  }();
+  const int forced = tune_overrides().epi_warps;
   if (forced == 4) return GEMM_THREADS;
   if (forced == 8) return GEMM_THREADS_MAX;
   return k_len_total <= 2048 ? GEMM_THREADS_MAX : GEMM_THREADS;
@@ -1549,13 +1544,10 @@ static int gather_maps(AMaps& a, const void* base, int64_t cols, int64_t rows, i
   return r;
 }
 
-// Largest run box in rows; FFNK_MAX_RUN_ROWS (0, 4, 8, ..., 128) overrides it for experiments.
+// Largest run box in rows (an override of 0, 4, 8, ..., 128 caps it).
 static int max_run_rows() {
-  static const int v = [] {
-    const char* e = getenv("FFNK_MAX_RUN_ROWS");
-    return e ? atoi(e) : BM;
-  }();
-  return v;
+  const int v = tune_overrides().max_run_rows;
+  return v >= 0 ? v : BM;
 }
 
 static long long* g_prof_buffer = nullptr;
@@ -1573,10 +1565,7 @@ static int usable_sms(const DeviceInfo& dev) {
 // M=32768) 8-16 row tiles 0.103 ms, 64 row tiles 0.109; single CTAs at K=4096 (gate/up) 32 row tiles
 // 2.07 ms, 16 row tiles 2.12, 8 row tiles 2.28.
 static int pick_group_m(int64_t k_len, bool pair = false) {
-  static const int forced = [] {
-    const char* e = getenv("FFNK_GROUP_M");
-    return e ? atoi(e) : 0;
-  }();
+  const int forced = tune_overrides().group_m;
   if (forced > 0) return forced;
   int64_t g = pair ? (16ll << 20) / (2 * BM * k_len * 2) : (32ll << 20) / (BM * k_len * 2);
   if (g < 4) g = 4;
@@ -1592,21 +1581,16 @@ static int pick_group_m(int64_t k_len, bool pair = false) {
 //   narrow : single CTAs with 64 accumulator columns, for problems with so few row tiles that 256-wide
 //            tiles would leave most SMs idle (small M: the weights then stream through 4x as many CTAs).
 //   else   : single CTAs, 128 x 256 tiles.
-// FFNK_PAIR=0/1 and FFNK_NARROW=0/1/2 (256-, 64-, 128-column tiles) override the choice for experiments.
+// ffnk_tune_override("pair", 0/1) and ("narrow", 0/1/2: 256-, 64-, 128-column tiles) replace the choice for a measurement.
 struct TileChoice {
   bool pair;
   int bn;   // accumulator columns per tile
 };
 
-static int env_flag(const char* name) {
-  const char* e = getenv(name);
-  return e ? atoi(e) : -1;
-}
-
 static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool k_major_weights,
                             int64_t k_len = int64_t(1) << 30) {
-  static const int force_pair = env_flag("FFNK_PAIR");
-  static const int force_narrow = env_flag("FFNK_NARROW");
+  const int force_pair = tune_overrides().pair;
+  const int force_narrow = tune_overrides().narrow;
   TileChoice t{false, BN};
   // Two-weight (SwiGLU) tiles go to pairs only when the four weights (8 d h bytes) stay in L2 and there
   // are many row tiles: the GEMM is then bound by L2 -> SM traffic, which a pair cuts by a third
@@ -1700,7 +1684,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
 // Average run length below which a routed-order copy beats gathering rows inside a GEMM with
 // `columns` output columns (see mask_is_scattered).
 static int copy_threshold(int64_t columns) {
-  static const int forced = env_flag("FFNK_COPY_THRESHOLD");   // experiments: run length below which copies are made
+  const int forced = tune_overrides().copy_threshold;
   if (forced >= 0) return forced;
   const int64_t t = columns / 6;
   return static_cast<int>(t < 32 ? 32 : (t > 4096 ? 4096 : t));
@@ -1725,8 +1709,8 @@ static int launch_wgrad(const void* P, int64_t ldp, int64_t p_dim, const void* Q
                  max_run_rows() < 64 ? max_run_rows() : 64, status, routed};
   wp.prof = g_prof_buffer;
   // operands in routed order and an output big enough for 256 x 256 tiles: the CTA-pair kernel
-  // (FFNK_WGRAD_PAIR=0/1 overrides for experiments)
-  static const int force_pair = env_flag("FFNK_WGRAD_PAIR");
+  // (ffnk_tune_override("wgrad_pair", 0/1) replaces the choice for a measurement)
+  const int force_pair = tune_overrides().wgrad_pair;
   const bool pair_ok = routed != 0;
   const bool pair = pair_ok && (force_pair >= 0 ? force_pair != 0 : (p_dim >= 256 && q_dim >= 128 && rows_total >= 1024));
   if (pair) {

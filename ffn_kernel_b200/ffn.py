@@ -52,7 +52,7 @@ def _phase(name: str) -> None:
 
 def permute_rows_first(M: int, d: int, h: int) -> bool:
     """Tile-table entry of the library for the FFN forward: is x copied into routed order before
-    the gate/up GEMM for this shape?  (FFNK_PERMUTE=0/1 overrides, read once per process.)"""
+    the gate/up GEMM for this shape?  (``ffnk_tune_override("permute", 0/1)`` replaces the choice.)"""
     return bool(lib().ffnk_ffn_permute_first(M, d, h))
 
 

@@ -236,6 +236,19 @@ int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, 
                     int64_t h, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Small-M MaskedFFN forward in one launch, for M <= ffnk_ffn_small_max_tokens() (127) and K-major
+ * weights: one persistent kernel streams each present modality's weights once (128-bit loads, the
+ * down-projection rows prefetched into L2 while gate/up runs) with a bounded grid-wide wait between
+ * the two phases; same contract as MaskedFFN.forward (ffn_kernel/ops.py:28-32), same arguments as
+ * ffnk_ffn_decode.  inter: scratch bf16 [M, h].  The launch is cooperative (all CTAs resident).
+ * ------------------------------------------------------------------------------------- */
+int ffnk_ffn_small_max_tokens(void);
+int ffnk_ffn_small(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
+                   const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n, int64_t w2_stride_k,
+                   int64_t w2_stride_n, const void* mask, void* inter, void* y, int64_t ldy, int64_t M, int64_t d,
+                   int64_t h, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * The whole MaskedFFN forward in one call (MaskedFFN.forward, ffn_kernel/ops.py:28-32):
  * routing, optional row permutation, gate/up, down -- or the decode kernels when
  * allow_decode != 0, M <= ffnk_decode_max_tokens() and the weights are K-major.
@@ -297,6 +310,13 @@ int ffnk_set_sm_margin(int sms);
  * [3] producer wait for a free stage, [4] producer total, [5] epilogue wait for an accumulator,
  * [6] epilogue total, [7] tiles.  Pass null to switch it off (the default).  Process-wide. */
 int ffnk_debug_profile_buffer(void* buffer);
+
+/* Diagnostics: replaces one entry of the compiled-in tile table so that a choice can be timed against its
+ * alternatives (`python -m ffn_kernel_b200.tune`; the reference searches its tile configurations offline,
+ * find_spec/find.py:18-64).  name: "pair", "narrow", "permute", "epi_warps", "group_m", "wgrad_pair",
+ * "max_run_rows", "copy_threshold", "verbose"; value -1 restores the table's own choice.  Process-wide,
+ * affects later launches; unknown names return FFNK_ERR_SHAPE.  The library reads no environment variables. */
+int ffnk_tune_override(const char* name, int value);
 
 /* Human-readable name of a return code or device status code (static storage). */
 const char* ffnk_status_string(int code);
