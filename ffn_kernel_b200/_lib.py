@@ -45,13 +45,10 @@ SIGNATURES = {
     "ffnk_sum_row_blocks_to_peers": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, POINTER(c_void_p),
                                              c_int, c_int64, c_int64, c_int, c_void_p]),
     "ffnk_decode_max_tokens": (c_int, []),
+    "ffnk_decode_capacity": (c_int, []),
     "ffnk_ffn_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p]),
-    "ffnk_ffn_small_max_tokens": (c_int, []),
-    "ffnk_ffn_small": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
-                               c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "ffnk_ffn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "ffnk_ffn_permute_first": (c_int, [c_int64, c_int64, c_int64]),
     "ffnk_ffn_forward": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIBDIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIBDIR, "libffnk.so")
-SOURCES = ("common.cu", "route.cu", "routed_gemm.cu", "decode.cu", "decode_fused.cu", "ffn_forward.cu", "tp_peers.cu")
+SOURCES = ("common.cu", "route.cu", "routed_gemm.cu", "decode_fused.cu", "ffn_forward.cu", "tp_peers.cu")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math"]
 

@@ -1,21 +1,22 @@
-// Small-M MaskedFFN forward in ONE launch: both phases (gate/up with the SiLU(t1)*t3 epilogue, then the
-// down projection) of up to 127 tokens, judged against HBM bandwidth: every weight of each modality
+// Small-M (decode) MaskedFFN forward in ONE launch: both phases (gate/up with the SiLU(t1)*t3 epilogue, then
+// the down projection) of up to 127 tokens, judged against HBM bandwidth: every weight of each modality
 // that has tokens is streamed exactly once (3*d*h bf16 per modality) by 128-bit loads.
 //
 // One persistent CTA per SM, 16 warps.  A work unit is 8 weight rows over the whole contraction
 // (gate and up rows of the same h index together in the first phase); the units of a phase are dealt
 // to the CTAs in contiguous, equally long ranges.  Inside a CTA the contraction is split over the 16
-// warps (k-blocks of 32 elements, warp w takes k-blocks w, w + 16, ...), loaded two steps ahead of
-// their use so that 64 KiB of weight loads per SM are in flight all the time.
+// warps (k-blocks of 32 elements, warp w takes k-blocks w, w + 16, ...), loaded two or three steps
+// ahead of their use so that 64-96 KiB of weight loads per SM are in flight.
 //   * the weights are the N = 8 side of mma.sync.m16n8k16 (bf16 in, fp32 accumulate), the modality's
 //     tokens, in groups of sixteen, the M = 16 side.  The k-slots of the instruction are assigned so
 //     that one 16-byte chunk of a weight row and the same chunk of two token rows feed two MMAs
 //     straight from registers, with no shuffles: lane (g, t) holds chunk t of weight row g and of
 //     tokens g and g + 8.
 //   * a unit ends with a shared-memory reduction over the warps in a fixed order (bitwise reproducible).
-//   * the phases are separated by a grid-wide arrive/wait on a counter in device memory (cooperative
-//     launch guarantees that all CTAs are resident; the wait is bounded and reports a status code).
-//     While the first phase runs, every CTA prefetches the down-projection rows it will need into L2.
+//   * the phases are separated by a grid-wide arrive/wait on a counter in device memory (one CTA per SM,
+//     so all CTAs are resident once earlier work has left the SMs; the wait is bounded and reports a
+//     status code).  While the first phase runs, every CTA prefetches the down-projection rows it will
+//     need into L2, and requests its first ones into registers before it waits.
 // tcgen05 is not used on purpose: with at most 127 rows a 128-row UMMA tile is mostly padding and the
 // weights would have to be staged through shared memory; the path is bound by the HBM stream.
 //
@@ -23,14 +24,16 @@
 // between the phases as in the reference (ffn_kernel/ffn.py:113).
 #include <cuda_bf16.h>
 
-#include <cstdlib>
-
 #include "ffnk_internal.h"
 #include "ptx.cuh"
 
 namespace ffnk {
 
-constexpr int kFusedMaxTokens = 127;
+constexpr int kFusedMaxTokens = 127;      // what the kernel can take
+// Up to this many tokens the tile table sends a forward here; beyond, the token rows (re-read from L2 by
+// every CTA) outweigh the weight stream and the tcgen05 GEMM path is faster (measured at d=1024/h=2816,
+// both modalities present: 64 tokens 30 us against 37 us, 96 tokens 37 us against 37 us, 127 tokens 50 against 38).
+constexpr int kDecodeTableTokens = 80;
 constexpr int kFusedWarps = 16;
 constexpr int kFusedThreads = kFusedWarps * 32;
 constexpr int kFusedBarrierSlots = 64;
@@ -91,55 +94,73 @@ struct StepLoads {
   uint4 b[GLU ? R : 1];
 };
 
+// Position of a pipeline step inside the CTA's work: pass over the token groups, unit, round of k-blocks.
+// Advanced incrementally (no divisions in the loop).
+struct StepCursor {
+  int round = 0, unit = 0, pass = 0;
+  __device__ __forceinline__ void advance(int rounds, int nunits) {
+    if (++round == rounds) {
+      round = 0;
+      if (++unit == nunits) {
+        unit = 0;
+        ++pass;
+      }
+    }
+  }
+};
+
 // One phase.  wa/wb: the (one or two) weights per modality, rows of `ldw` elements; xin rows of ldx
 // elements (the activations, or the intermediate); out[token][row].
 //   G: token groups of sixteen held in accumulators at a time; a modality with more tokens takes several
 //      passes over the CTA's units (the second pass finds the weights in L2).
-//   R: k-blocks a warp loads per step;  D: steps whose loads are in flight (D * R * 16 or 32 bytes per lane).
-// A unit is 8 weight rows, or 4 (half of the lanes idle) when 8-row units would leave the CTAs with
-// fewer than four units each and the split uneven.
-template <bool GLU, int G, int R, int D>
+//   R: k-blocks a warp loads per step;  D (2 or 3): steps whose loads are in flight.
+// `before_consume` runs once after the first D steps' weight loads have been issued and before anything
+// is multiplied: the place to wait for whatever the token rows depend on (it returns false to give up).
+template <bool GLU, int G, int R, int D, typename Hook>
 __device__ __forceinline__ void run_phase(const __nv_bfloat16* const (&wa)[2], const __nv_bfloat16* const (&wb)[2],
                                           int64_t ldw, const __nv_bfloat16* xin, int64_t ldx, int K, int rows,
-                                          __nv_bfloat16* out, int64_t ldo, const int (&ntok)[2],
-                                          const int (*s_tok)[128], float* s_part, bool x_from_l2) {
+                                          __nv_bfloat16* out, int64_t ldo, int ntok0, int ntok1,
+                                          const int (*s_tok)[128], float* s_part, Hook&& before_consume) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int present0 = ntok[0] > 0 ? 1 : 0, present1 = ntok[1] > 0 ? 1 : 0;
-  const int rpu = ((present0 + present1) * (rows >> 3) < 4 * static_cast<int>(gridDim.x) && (rows & 3) == 0) ? 4 : 8;
-  const int units_per_mod = rows / rpu;
+  const int present0 = ntok0 > 0 ? 1 : 0, present1 = ntok1 > 0 ? 1 : 0;
+  const int units_per_mod = rows >> 3;
   const int units = (present0 + present1) * units_per_mod;
   const int u0 = static_cast<int>(static_cast<long long>(blockIdx.x) * units / gridDim.x);
   const int u1 = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * units / gridDim.x);
   const int nunits = u1 - u0;
-  if (nunits <= 0) return;
+  if (nunits <= 0) {          // a CTA without work still takes part in whatever the hook waits for
+    before_consume();
+    return;
+  }
   const int kblocks = (K + 31) >> 5;
   const int rounds = (kblocks + kFusedWarps * R - 1) / (kFusedWarps * R);
-  const int max_tok = max(ntok[0], ntok[1]);
+  const int max_tok = max(ntok0, ntok1);
   const int passes = (max_tok + 16 * G - 1) / (16 * G);
   const int steps = passes * nunits * rounds;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  const bool row_lane = g < rpu;      // this lane's weight row exists in the unit
+  const int k_lane = warp * 32 + t * 8;                 // this lane's column in the first k-block of a round
+  constexpr int K_ROUND = kFusedWarps * 32;             // columns the 16 warps cover per k-block index
 
-  auto unit_of = [&](int s, int& m, int& rb, int& round, int& pass) {
-    round = s % rounds;
-    const int ul = (s / rounds) % nunits;
-    pass = s / (rounds * nunits);
+  // modality and first row of unit `ul` of this CTA
+  auto unit_rows = [&](int ul, int& m, int& row0) {
     const int u = u0 + ul;
-    const int which = u / units_per_mod;             // index among the modalities present
-    m = present0 ? which : 1;
-    rb = u - which * units_per_mod;
+    const int second = (present0 && u >= units_per_mod) ? 1 : 0;
+    m = present0 ? second : 1;
+    row0 = (u - second * units_per_mod) << 3;
   };
-  auto load_step = [&](int s, StepLoads<GLU, R>& L) {
-    int m, rb, round, pass;
-    unit_of(s, m, rb, round, pass);
-    const int64_t row_off = static_cast<int64_t>(rb * rpu + g) * ldw;
+  auto load_step = [&](const StepCursor& c, StepLoads<GLU, R>& L) {
+    int m, row0;
+    unit_rows(c.unit, m, row0);
+    const int kbase = k_lane + c.round * (R * K_ROUND);
+    const int64_t off = static_cast<int64_t>(row0 + g) * ldw + kbase;
+    const __nv_bfloat16* pa = (m ? wa[1] : wa[0]) + off;
+    const __nv_bfloat16* pb = GLU ? (m ? wb[1] : wb[0]) + off : nullptr;
 #pragma unroll
     for (int j = 0; j < R; ++j) {
-      const int k = ((round * R + j) * kFusedWarps + warp) * 32 + t * 8;
-      const bool ok = row_lane && k < K;
-      L.a[j] = ok ? ldg_stream_16(wa[m] + row_off + k) : zero;
-      if constexpr (GLU) L.b[j] = ok ? ldg_stream_16(wb[m] + row_off + k) : zero;
+      const bool ok = kbase + j * K_ROUND < K;
+      L.a[j] = ok ? ldg_stream_16(pa + j * K_ROUND) : zero;
+      if constexpr (GLU) L.b[j] = ok ? ldg_stream_16(pb + j * K_ROUND) : zero;
     }
   };
 
@@ -151,51 +172,82 @@ __device__ __forceinline__ void run_phase(const __nv_bfloat16* const (&wa)[2], c
       acc_a[gi][i] = 0.f;
       if (GLU) acc_b[gi][i] = 0.f;
     }
-  int pb = 0;   // which half of the double-buffered partial sums
 
-  auto consume = [&](int s, const StepLoads<GLU, R>& cur) {
-    int m, rb, round, pass;
-    unit_of(s, m, rb, round, pass);
-    const int nt = ntok[m];
-    const int groups_left = (nt - pass * 16 * G + 15) >> 4;     // may be <= 0: nothing to do in this pass
+  // multiply-accumulate one step's weights with the token rows of the unit's modality
+  auto mma_step = [&](const StepCursor& c, const StepLoads<GLU, R>& W, int m, int nt) {
+    const int kbase = k_lane + c.round * (R * K_ROUND);
 #pragma unroll
     for (int gi = 0; gi < G; ++gi) {
-      if (gi < groups_left) {
-        const int slot_lo = (pass * G + gi) * 16 + g, slot_hi = slot_lo + 8;
-        const __nv_bfloat16* xlo = slot_lo < nt ? xin + static_cast<int64_t>(s_tok[m][slot_lo]) * ldx : nullptr;
-        const __nv_bfloat16* xhi = slot_hi < nt ? xin + static_cast<int64_t>(s_tok[m][slot_hi]) * ldx : nullptr;
+      const int slot_lo = (c.pass * G + gi) * 16 + g, slot_hi = slot_lo + 8;
+      if ((c.pass * G + gi) * 16 < nt) {                     // warp-uniform: the group has tokens
+        const __nv_bfloat16* xlo = slot_lo < nt ? xin + static_cast<int64_t>(s_tok[m][slot_lo]) * ldx + kbase : nullptr;
+        const __nv_bfloat16* xhi = slot_hi < nt ? xin + static_cast<int64_t>(s_tok[m][slot_hi]) * ldx + kbase : nullptr;
         uint4 vlo[R], vhi[R];
 #pragma unroll
         for (int j = 0; j < R; ++j) {
-          const int k = ((round * R + j) * kFusedWarps + warp) * 32 + t * 8;
-          const bool ok = k < K;
-          vlo[j] = vhi[j] = zero;
-          if (ok && xlo) vlo[j] = x_from_l2 ? ldg_cg_16(xlo + k) : *reinterpret_cast<const uint4*>(xlo + k);
-          if (ok && xhi) vhi[j] = x_from_l2 ? ldg_cg_16(xhi + k) : *reinterpret_cast<const uint4*>(xhi + k);
+          const bool ok = kbase + j * K_ROUND < K;
+          vlo[j] = (ok && xlo) ? *reinterpret_cast<const uint4*>(xlo + j * K_ROUND) : zero;
+          vhi[j] = (ok && xhi) ? *reinterpret_cast<const uint4*>(xhi + j * K_ROUND) : zero;
         }
 #pragma unroll
         for (int j = 0; j < R; ++j) {
-          mma_tok16_row8(acc_a[gi], vlo[j].x, vhi[j].x, vlo[j].y, vhi[j].y, cur.a[j].x, cur.a[j].y);
-          mma_tok16_row8(acc_a[gi], vlo[j].z, vhi[j].z, vlo[j].w, vhi[j].w, cur.a[j].z, cur.a[j].w);
+          mma_tok16_row8(acc_a[gi], vlo[j].x, vhi[j].x, vlo[j].y, vhi[j].y, W.a[j].x, W.a[j].y);
+          mma_tok16_row8(acc_a[gi], vlo[j].z, vhi[j].z, vlo[j].w, vhi[j].w, W.a[j].z, W.a[j].w);
           if constexpr (GLU) {
-            mma_tok16_row8(acc_b[gi], vlo[j].x, vhi[j].x, vlo[j].y, vhi[j].y, cur.b[j].x, cur.b[j].y);
-            mma_tok16_row8(acc_b[gi], vlo[j].z, vhi[j].z, vlo[j].w, vhi[j].w, cur.b[j].z, cur.b[j].w);
+            mma_tok16_row8(acc_b[gi], vlo[j].x, vhi[j].x, vlo[j].y, vhi[j].y, W.b[j].x, W.b[j].y);
+            mma_tok16_row8(acc_b[gi], vlo[j].z, vhi[j].z, vlo[j].w, vhi[j].w, W.b[j].z, W.b[j].w);
           }
         }
       }
     }
-    if (round == rounds - 1) {
-      // the unit is complete in this warp: publish the partial sums, add the 16 warps' in warp order
-      float* part = s_part + pb * (kFusedWarps * G * 256);
-      if (groups_left > 0) {
+  };
+
+  StepLoads<GLU, R> buf0, buf1, buf2;
+  auto with_slot = [&](int sl, auto&& f) {
+    if (sl == 0) f(buf0);
+    else if (D == 2 || sl == 1) f(buf1);
+    else f(buf2);
+  };
+  StepCursor lc, cc;                 // load cursor (D steps ahead), consume cursor
 #pragma unroll
-        for (int gi = 0; gi < G; ++gi) {
-          if (gi < groups_left) {
-            float* mine = part + ((warp * G + gi) * 32 + lane) * 8;
-            *reinterpret_cast<float4*>(mine) = make_float4(acc_a[gi][0], acc_a[gi][1], acc_a[gi][2], acc_a[gi][3]);
-            if constexpr (GLU)
-              *reinterpret_cast<float4*>(mine + 4) = make_float4(acc_b[gi][0], acc_b[gi][1], acc_b[gi][2], acc_b[gi][3]);
-          }
+  for (int i = 0; i < D; ++i) {
+    if (i < steps) {
+      with_slot(i, [&](StepLoads<GLU, R>& b) { load_step(lc, b); });
+      lc.advance(rounds, nunits);
+    }
+  }
+  if (!before_consume()) return;
+  int pb = 0;   // which half of the double-buffered partial sums
+  int sl = 0;   // slot of the step being consumed
+#pragma unroll 1
+  for (int s = 0; s < steps; ++s) {
+    int m, row0;
+    unit_rows(cc.unit, m, row0);
+    const int nt = m ? ntok1 : ntok0;
+    with_slot(sl, [&](StepLoads<GLU, R>& b) {
+      mma_step(cc, b, m, nt);
+      if (s + D < steps) {
+        load_step(lc, b);
+        lc.advance(rounds, nunits);
+      }
+    });
+    if (++sl == D) sl = 0;
+    if (cc.round == rounds - 1) {
+      // the unit is complete in this warp: publish the partial sums, add the 16 warps' in warp order
+      const int groups_left = (nt - cc.pass * 16 * G + 15) >> 4;     // may be <= 0: nothing to do in this pass
+      float* part = s_part + pb * (kFusedWarps * G * 256);
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi) {
+        if (gi < groups_left) {
+          float* mine = part + ((warp * G + gi) * 32 + lane) * 8;
+          *reinterpret_cast<float4*>(mine) = make_float4(acc_a[gi][0], acc_a[gi][1], acc_a[gi][2], acc_a[gi][3]);
+          if constexpr (GLU)
+            *reinterpret_cast<float4*>(mine + 4) = make_float4(acc_b[gi][0], acc_b[gi][1], acc_b[gi][2], acc_b[gi][3]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc_a[gi][i] = 0.f;
+          if (GLU) acc_b[gi][i] = 0.f;
         }
       }
       __syncthreads();
@@ -211,37 +263,15 @@ __device__ __forceinline__ void run_phase(const __nv_bfloat16* const (&wa)[2], c
           va += col[w * G * 256];
           if constexpr (GLU) vb += col[w * G * 256 + 4];
         }
-        const int slot = (pass * G + gi) * 16 + tau;
-        if (slot < nt && rho < rpu) {
+        const int slot = (cc.pass * G + gi) * 16 + tau;
+        if (slot < nt) {
           if constexpr (GLU) va = va * __frcp_rn(1.0f + __expf(-va)) * vb;
-          out[static_cast<int64_t>(s_tok[m][slot]) * ldo + rb * rpu + rho] = __float2bfloat16_rn(va);
+          out[static_cast<int64_t>(s_tok[m][slot]) * ldo + row0 + rho] = __float2bfloat16_rn(va);
         }
       }
       pb ^= 1;
-#pragma unroll
-      for (int gi = 0; gi < G; ++gi)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc_a[gi][i] = 0.f;
-          if (GLU) acc_b[gi][i] = 0.f;
-        }
     }
-  };
-
-  StepLoads<GLU, R> buf[D];
-#pragma unroll
-  for (int i = 0; i < D; ++i)
-    if (i < steps) load_step(i, buf[i]);
-#pragma unroll 1
-  for (int s0 = 0; s0 < steps; s0 += D) {
-#pragma unroll
-    for (int i = 0; i < D; ++i) {
-      const int s = s0 + i;
-      if (s < steps) {
-        consume(s, buf[i]);
-        if (s + D < steps) load_step(s + D, buf[i]);
-      }
-    }
+    cc.advance(rounds, nunits);
   }
 }
 
@@ -249,45 +279,38 @@ template <int G>
 __global__ void __launch_bounds__(kFusedThreads, 1) decode_fused_kernel(const FusedParams p) {
   extern __shared__ float s_part[];          // [2][16 warps][G][32 lanes][8]
   __shared__ int s_tok[2][128];
-  __shared__ int s_wcnt[2][4];
   __shared__ int s_ok;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // token lists of the two modalities, ascending
-  if (warp < 4) {
-    const int idx = warp * 32 + lane;
-    const bool valid = idx < p.M;
-    const bool vis = valid && p.mask[idx] != 0;
-    const uint32_t bv = __ballot_sync(0xFFFFFFFFu, vis), bt = __ballot_sync(0xFFFFFFFFu, valid && !vis);
-    if (lane == 0) {
-      s_wcnt[0][warp] = __popc(bv);
-      s_wcnt[1][warp] = __popc(bt);
-    }
-    __syncwarp();
-  }
-  __syncthreads();
+  // Token lists of the two modalities, ascending.  Every warp reads the (at most 127) mask bytes and counts
+  // for itself, so nobody waits for a barrier before the first weight loads go out; warp 0 also writes the
+  // lists, which are first read after the barrier that follows those loads.
   int ntok[2] = {0, 0};
+  {
+    uint32_t bv[4], bt[4];
 #pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    ntok[0] += s_wcnt[0][w];
-    ntok[1] += s_wcnt[1][w];
-  }
-  if (warp < 4) {
-    const int idx = warp * 32 + lane;
-    const bool valid = idx < p.M;
-    const bool vis = valid && p.mask[idx] != 0;
-    const uint32_t bv = __ballot_sync(0xFFFFFFFFu, vis), bt = __ballot_sync(0xFFFFFFFFu, valid && !vis);
-    int off_v = 0, off_t = 0;
-    for (int w = 0; w < warp; ++w) {
-      off_v += s_wcnt[0][w];
-      off_t += s_wcnt[1][w];
+    for (int j = 0; j < 4; ++j) {
+      const int idx = j * 32 + lane;
+      const bool valid = idx < p.M;
+      const bool vis = valid && p.mask[idx] != 0;
+      bv[j] = __ballot_sync(0xFFFFFFFFu, vis);
+      bt[j] = __ballot_sync(0xFFFFFFFFu, valid && !vis);
+      ntok[0] += __popc(bv[j]);
+      ntok[1] += __popc(bt[j]);
     }
-    const uint32_t below = (1u << lane) - 1u;
-    if (vis) s_tok[0][off_v + __popc(bv & below)] = idx;
-    else if (valid) s_tok[1][off_t + __popc(bt & below)] = idx;
+    if (warp == 0) {
+      const uint32_t below = (1u << lane) - 1u;
+      int off_v = 0, off_t = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if ((bv[j] >> lane) & 1u) s_tok[0][off_v + __popc(bv[j] & below)] = j * 32 + lane;
+        if ((bt[j] >> lane) & 1u) s_tok[1][off_t + __popc(bt[j] & below)] = j * 32 + lane;
+        off_v += __popc(bv[j]);
+        off_t += __popc(bt[j]);
+      }
+    }
+    if (threadIdx.x == 0) s_ok = 1;
   }
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
 
   // second-phase weights of this CTA's share of rows into L2 while the first phase streams
   {
@@ -296,50 +319,57 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_fused_kernel(const Fu
     const int r0 = static_cast<int>(static_cast<long long>(blockIdx.x) * rows_all / gridDim.x) & ~7;
     const int r1 = min(rows_all, (static_cast<int>(static_cast<long long>(blockIdx.x + 1) * rows_all / gridDim.x) + 7) & ~7);
     const int lines_per_row = (p.h * 2) >> 7;   // whole 128-byte lines inside the row
-    const int total = (r1 - r0) * lines_per_row;
-    for (int i = threadIdx.x; i < total; i += kFusedThreads) {
-      const int line = i % lines_per_row;
-      const int r = r0 + i / lines_per_row;
-      const int which = r / p.d;
-      const int m = present0 ? which : 1;
-      prefetch_l2(reinterpret_cast<const char*>(p.down[m] + static_cast<int64_t>(r - which * p.d) * p.ld2) + line * 128);
+    for (int r = r0 + warp; r < r1; r += kFusedWarps) {
+      const int second = r >= p.d ? 1 : 0;
+      const int m = present0 ? second : 1;
+      const char* row = reinterpret_cast<const char*>(p.down[m] + static_cast<int64_t>(r - second * p.d) * p.ld2);
+      for (int line = lane; line < lines_per_row; line += 32) prefetch_l2(row + line * 128);
     }
   }
 
   const __nv_bfloat16* const none[2] = {nullptr, nullptr};
-  run_phase<true, G, 2, (G <= 2 ? 4 : 2)>(p.gate, p.up, p.ld13, p.x, p.ldx, p.d, p.h, p.inter, static_cast<int64_t>(p.h),
-                                          ntok, s_tok, s_part, false);
+  constexpr int DEPTH = G <= 2 ? 3 : 2;
+  run_phase<true, G, 2, DEPTH>(p.gate, p.up, p.ld13, p.x, p.ldx, p.d, p.h, p.inter, static_cast<int64_t>(p.h), ntok[0],
+                               ntok[1], s_tok, s_part, [&]() -> bool {
+                                 __syncthreads();      // the token lists are in shared memory
+                                 return true;
+                               });
 
-  // every CTA's part of the intermediate is written: arrive, then wait for the whole grid
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    unsigned long long* bar = &g_fused_barrier[p.slot];
-    const unsigned long long ticket = atomicAdd(bar, 1ULL);
-    const unsigned long long target = (ticket / gridDim.x + 1ULL) * gridDim.x;
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t polls = 0;
-    while (ld_acquire_gpu_u64(bar) < target) {
-      if ((++polls & 63u) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
-        if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_GRID);
-        s_ok = 0;
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  if (!s_ok) return;
-  run_phase<false, G, 3, (G <= 2 ? 4 : 2)>(p.down, none, p.ld2, p.inter, static_cast<int64_t>(p.h), p.h, p.d, p.y, p.ldy,
-                                           ntok, s_tok, s_part, true);
+  // The first down-projection weights are requested before the wait (they do not depend on the first
+  // phase); then every CTA's part of the intermediate must be written: arrive, wait for the whole grid.
+  // The intermediate was written by other SMs before that wait and has never been read by this one, so
+  // ordinary (L1-allocating) loads cannot see stale lines.
+  run_phase<false, G, 3, DEPTH>(p.down, none, p.ld2, p.inter, static_cast<int64_t>(p.h), p.h, p.d, p.y, p.ldy, ntok[0],
+                                ntok[1], s_tok, s_part, [&]() -> bool {
+                                  __syncthreads();
+                                  if (threadIdx.x == 0) {
+                                    __threadfence();
+                                    unsigned long long* bar = &g_fused_barrier[p.slot];
+                                    const unsigned long long ticket = atomicAdd(bar, 1ULL);
+                                    const unsigned long long target = (ticket / gridDim.x + 1ULL) * gridDim.x;
+                                    const uint64_t t0 = globaltimer_ns();
+                                    uint32_t polls = 0;
+                                    while (ld_acquire_gpu_u64(bar) < target) {
+                                      if ((++polls & 63u) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+                                        if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_GRID);
+                                        s_ok = 0;
+                                        break;
+                                      }
+                                    }
+                                  }
+                                  __syncthreads();
+                                  return s_ok != 0;
+                                });
 }
 
 }  // namespace ffnk
 
 using namespace ffnk;
 
-extern "C" int ffnk_ffn_small_max_tokens(void) { return kFusedMaxTokens; }
+extern "C" int ffnk_decode_max_tokens(void) { return kDecodeTableTokens; }
+extern "C" int ffnk_decode_capacity(void) { return kFusedMaxTokens; }
 
-extern "C" int ffnk_ffn_small(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
+extern "C" int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
                               const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n,
                               int64_t w2_stride_k, int64_t w2_stride_n, const void* mask, void* inter, void* y,
                               int64_t ldy, int64_t M, int64_t d, int64_t h, int32_t* status, void* stream_) {
@@ -382,16 +412,12 @@ extern "C" int ffnk_ffn_small(const void* x, int64_t ldx, const void* w1, const 
 
   const int G = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
   const size_t smem = static_cast<size_t>(2) * kFusedWarps * G * 256 * sizeof(float);
-  void* args[] = {&p};
   auto go = [&](auto kernel) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return cuda_status(e);
-    static const bool coop = getenv("FFNK_COOP") != nullptr;
-    if (coop) {
-      e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(dev.sm_count), dim3(kFusedThreads), args, smem,
-                                      stream);
-      return cuda_status(e);
-    }
+    // An ordinary launch: one CTA per SM of 512 threads and at most 128 KiB of shared memory always fits, so
+    // every CTA becomes resident as soon as the SMs are free of earlier work, and the grid-wide wait (bounded
+    // in any case) cannot starve a CTA that has not started.
     kernel<<<dev.sm_count, kFusedThreads, smem, stream>>>(p);
     return cuda_status(cudaGetLastError());
   };

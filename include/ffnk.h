@@ -225,32 +225,23 @@ int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int64_t block_
                                  int max_ctas, void* stream);
 
 /* ---------------------------------------------------------------------------------------
- * Small-M (decode) MaskedFFN forward: streams each present modality's weights once with
- * 128-bit loads; same contract as MaskedFFN.forward (ffn_kernel/ops.py:28-32).
- * inter: scratch bf16 [M, h].  Supported for M <= ffnk_decode_max_tokens() (32) and K-major weights.
+ * Small-M (decode) MaskedFFN forward in one launch, judged against HBM bandwidth: one persistent kernel
+ * streams each present modality's weights once with 128-bit loads (the down-projection rows prefetched
+ * into L2 while gate/up runs), with a bounded grid-wide wait between the two phases.  Same contract as
+ * MaskedFFN.forward (ffn_kernel/ops.py:28-32).  inter: scratch bf16 [M, h].  K-major weights only.
+ * Accepts M <= ffnk_decode_capacity() (127); ffnk_decode_max_tokens() (80) is the tile table's threshold:
+ * up to it ffnk_ffn_forward takes this path, beyond it the GEMM path is faster.
  * ------------------------------------------------------------------------------------- */
 int ffnk_decode_max_tokens(void);
+int ffnk_decode_capacity(void);
 int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
                     const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n, int64_t w2_stride_k,
                     int64_t w2_stride_n, const void* mask, void* inter, void* y, int64_t ldy, int64_t M, int64_t d,
                     int64_t h, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------
- * Small-M MaskedFFN forward in one launch, for M <= ffnk_ffn_small_max_tokens() (127) and K-major
- * weights: one persistent kernel streams each present modality's weights once (128-bit loads, the
- * down-projection rows prefetched into L2 while gate/up runs) with a bounded grid-wide wait between
- * the two phases; same contract as MaskedFFN.forward (ffn_kernel/ops.py:28-32), same arguments as
- * ffnk_ffn_decode.  inter: scratch bf16 [M, h].  The launch is cooperative (all CTAs resident).
- * ------------------------------------------------------------------------------------- */
-int ffnk_ffn_small_max_tokens(void);
-int ffnk_ffn_small(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
-                   const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n, int64_t w2_stride_k,
-                   int64_t w2_stride_n, const void* mask, void* inter, void* y, int64_t ldy, int64_t M, int64_t d,
-                   int64_t h, int32_t* status, void* stream);
-
-/* ---------------------------------------------------------------------------------------
  * The whole MaskedFFN forward in one call (MaskedFFN.forward, ffn_kernel/ops.py:28-32):
- * routing, optional row permutation, gate/up, down -- or the decode kernels when
+ * routing, optional row permutation, gate/up, down -- or the decode kernel when
  * allow_decode != 0, M <= ffnk_decode_max_tokens() and the weights are K-major.
  * workspace: ffnk_ffn_workspace_bytes(M, d, h) bytes of device memory, 256-byte aligned, owned by
  * the caller and reusable as soon as the stream has passed this call; too small a workspace

@@ -59,7 +59,8 @@ def test_argument_errors_are_reported_before_any_launch(libffnk):
     # misaligned leading dimension
     assert L.ffnk_linear_fwd(fake, 9, fake, fake, 1, 8, fake, fake, fake, 8, None, 16, 8, 8, fake, None) == -3
     # decode: too many tokens, wrong weight layout
-    n = L.ffnk_decode_max_tokens()
+    n = L.ffnk_decode_capacity()
+    assert 1 <= L.ffnk_decode_max_tokens() <= n
     args = [fake, 8, fake, fake, fake, fake, fake, fake, 1, 8, 1, 8, fake, fake, fake, 8]
     assert L.ffnk_ffn_decode(*args, n + 1, 8, 8, fake, None) == -2
     args[8], args[9] = 8, 1
