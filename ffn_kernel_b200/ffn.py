@@ -64,7 +64,7 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
                             allow_decode: bool = True):
     """The full forward: y[m] = (silu(x[m] W1) * (x[m] W3)) W2 with the modality's weights.
 
-    Small token counts take the weight-streaming decode kernels, everything else the two
+    Small token counts take the weight-streaming decode kernel, everything else the two
     routed GEMMs.  Argument order follows ``MaskedFFN.apply`` (``ffn_kernel/ops.py:30``)."""
     x = _activation(x, "x")
     M, d = x.shape
@@ -81,7 +81,7 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
         st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
         if rt is None and PHASE_HOOK is None:
             # the normal path: one call into the library does routing, permutation and both GEMMs
-            # (or the decode kernels) out of one workspace allocation
+            # (or the decode kernel) out of one workspace allocation
             if mask.dim() != 1 or mask.shape[0] != M or mask.device != dev:
                 raise RuntimeError(f"mask must have shape [{M}] on {dev}")
             if mask.dtype not in (torch.bool, torch.uint8):

@@ -234,7 +234,7 @@ def main():
                 _bf16_ffn_fused_forward(*ar)
         t = timeit(g.replay, a.iters, a.warmup) / n_sets
         present = (1 if bool(cases[0].mask.any()) else 0) + (1 if bool((~cases[0].mask).any()) else 0)
-        emit(kernel="ffn_decode(2 launches)", M=M, d=d, h=h, mask=a.mask, ms=t, weight_sets=n_sets,
+        emit(kernel="ffn_decode(one launch)", M=M, d=d, h=h, mask=a.mask, ms=t, weight_sets=n_sets,
              gbs=present * 3 * d * h * 2 / t / 1e6)
     check_status()
 

@@ -47,10 +47,10 @@ def test_edge_and_decode_sweep(dev, M, kind):
     assert O.max_rel_err(y, ref) < TOL
 
 
-@pytest.mark.parametrize("M", [9, 16, 17, 24, 25, 32])
+@pytest.mark.parametrize("M", [9, 16, 17, 24, 25, 32, 33, 47, 64, 80])
 @pytest.mark.parametrize("kind", ["all_visual", "all_text", "alternating", "bernoulli"])
 def test_decode_kernels_token_groups(dev, M, kind):
-    # more than eight tokens: several groups of eight per modality, partly filled last group
+    # several groups of sixteen tokens per modality, partly filled last group
     assert M <= decode_max_tokens()
     c = ffn_case(M, 264, 520, seed=M, mask=edge_mask(M, kind, seed=2))
     ref = O.masked_ffn(*c.apply_args())
@@ -59,7 +59,34 @@ def test_decode_kernels_token_groups(dev, M, kind):
     assert O.max_rel_err(y, ref) < TOL
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 20, 32])
+@pytest.mark.parametrize("M", [33, 48, 64, 65, 80, 96, 127])
+@pytest.mark.parametrize("kind", ["all_visual", "all_text", "alternating", "bernoulli"])
+@pytest.mark.parametrize("d,h", [(264, 520), (1024, 2816)])
+def test_decode_kernel_up_to_its_capacity(dev, M, kind, d, h):
+    # the one-launch kernel through the C ABI beyond the table's threshold: up to 127 tokens, more than
+    # four groups of sixteen in one modality (a second pass over the weights), ragged last groups;
+    # two calls in a row give the same bits (fixed summation order)
+    from ffn_kernel_b200._lib import lib
+    from ffn_kernel_b200.route import status_word, stream_ptr
+    L = lib()
+    assert M <= L.ffnk_decode_capacity()
+    c = ffn_case(M, d, h, seed=M + d, mask=edge_mask(M, kind, seed=3))
+    ref = O.masked_ffn(*c.apply_args())
+    g = c.to(dev)
+    ys = []
+    for _ in range(2):
+        inter = torch.full((M, h), float("nan"), device=dev, dtype=torch.bfloat16)
+        y = torch.full((M, d), float("nan"), device=dev, dtype=torch.bfloat16)
+        assert L.ffnk_ffn_decode(g.x.data_ptr(), d, g.w1.data_ptr(), g.w2.data_ptr(), g.w3.data_ptr(), g.u1.data_ptr(),
+                                 g.u2.data_ptr(), g.u3.data_ptr(), 1, d, 1, h, g.mask.data_ptr(), inter.data_ptr(),
+                                 y.data_ptr(), d, M, d, h, status_word(dev).data_ptr(), stream_ptr(dev)) == 0
+        ys.append(y)
+    check_status()
+    assert O.max_rel_err(ys[0], ref) < TOL
+    assert torch.equal(ys[0], ys[1])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 20, 32, 50, 80])
 def test_decode_and_gemm_paths_agree(dev, M):
     assert M <= decode_max_tokens()
     c = ffn_case(M, 256, 520, seed=M, mask=edge_mask(M, "alternating")).to(dev)
