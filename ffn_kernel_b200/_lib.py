@@ -46,6 +46,7 @@ SIGNATURES = {
                                              c_int, c_int64, c_int64, c_int, c_void_p]),
     "ffnk_decode_max_tokens": (c_int, []),
     "ffnk_decode_capacity": (c_int, []),
+    "ffnk_ffn_takes_decode": (c_int, [c_int64, c_int64, c_int64]),
     "ffnk_ffn_decode": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                                 c_int64, c_int64, c_int64, c_void_p, c_void_p]),

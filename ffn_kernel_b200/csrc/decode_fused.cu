@@ -57,6 +57,7 @@ struct FusedParams {
   int M, d, h;
   int slot;
   int* status;
+  long long* prof;                // optional per-CTA cycle stamps (8 per CTA), see ffnk_debug_profile_buffer
 };
 
 __device__ __forceinline__ uint4 ldg_stream_16(const void* p) {
@@ -126,8 +127,9 @@ __device__ __forceinline__ void run_phase(const __nv_bfloat16* const (&wa)[2], c
   const int present0 = ntok0 > 0 ? 1 : 0, present1 = ntok1 > 0 ? 1 : 0;
   const int units_per_mod = rows >> 3;
   const int units = (present0 + present1) * units_per_mod;
-  const int u0 = static_cast<int>(static_cast<long long>(blockIdx.x) * units / gridDim.x);
-  const int u1 = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * units / gridDim.x);
+  // (units < 2^22 and at most a few hundred CTAs: the products fit 32 bits)
+  const int u0 = static_cast<int>(blockIdx.x * static_cast<unsigned>(units) / gridDim.x);
+  const int u1 = static_cast<int>((blockIdx.x + 1u) * static_cast<unsigned>(units) / gridDim.x);
   const int nunits = u1 - u0;
   if (nunits <= 0) {          // a CTA without work still takes part in whatever the hook waits for
     before_consume();
@@ -281,6 +283,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_fused_kernel(const Fu
   __shared__ int s_tok[2][128];
   __shared__ int s_ok;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long* prof = p.prof ? p.prof + blockIdx.x * 8 : nullptr;
+  const long long c_start = clock64();
+  auto stamp = [&](int i) {
+    if (prof && threadIdx.x == 0) prof[i] = clock64() - c_start;
+  };
 
   // Token lists of the two modalities, ascending.  Every warp reads the (at most 127) mask bytes and counts
   // for itself, so nobody waits for a barrier before the first weight loads go out; warp 0 also writes the
@@ -311,13 +318,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_fused_kernel(const Fu
     }
     if (threadIdx.x == 0) s_ok = 1;
   }
+  stamp(0);          // mask read, tokens counted
 
-  // second-phase weights of this CTA's share of rows into L2 while the first phase streams
-  {
+  // second-phase weights of this CTA's share of rows into L2 while the first phase streams (issued
+  // behind the first gate/up loads, which are what the CTA waits for first)
+  auto prefetch_down_rows = [&]() {
     const int present0 = ntok[0] > 0 ? 1 : 0, present1 = ntok[1] > 0 ? 1 : 0;
     const int rows_all = (present0 + present1) * p.d;
-    const int r0 = static_cast<int>(static_cast<long long>(blockIdx.x) * rows_all / gridDim.x) & ~7;
-    const int r1 = min(rows_all, (static_cast<int>(static_cast<long long>(blockIdx.x + 1) * rows_all / gridDim.x) + 7) & ~7);
+    const int u_all = rows_all >> 3;
+    const int r0 = static_cast<int>(blockIdx.x * static_cast<unsigned>(u_all) / gridDim.x) << 3;
+    const int r1 = static_cast<int>((blockIdx.x + 1u) * static_cast<unsigned>(u_all) / gridDim.x) << 3;
     const int lines_per_row = (p.h * 2) >> 7;   // whole 128-byte lines inside the row
     for (int r = r0 + warp; r < r1; r += kFusedWarps) {
       const int second = r >= p.d ? 1 : 0;
@@ -325,15 +335,18 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_fused_kernel(const Fu
       const char* row = reinterpret_cast<const char*>(p.down[m] + static_cast<int64_t>(r - second * p.d) * p.ld2);
       for (int line = lane; line < lines_per_row; line += 32) prefetch_l2(row + line * 128);
     }
-  }
+  };
 
   const __nv_bfloat16* const none[2] = {nullptr, nullptr};
   constexpr int DEPTH = G <= 2 ? 3 : 2;
   run_phase<true, G, 2, DEPTH>(p.gate, p.up, p.ld13, p.x, p.ldx, p.d, p.h, p.inter, static_cast<int64_t>(p.h), ntok[0],
                                ntok[1], s_tok, s_part, [&]() -> bool {
+                                 stamp(1);             // first gate/up weights requested
+                                 prefetch_down_rows();
                                  __syncthreads();      // the token lists are in shared memory
                                  return true;
                                });
+  stamp(2);          // gate/up done in this CTA
 
   // The first down-projection weights are requested before the wait (they do not depend on the first
   // phase); then every CTA's part of the intermediate must be written: arrive, wait for the whole grid.
@@ -342,6 +355,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_fused_kernel(const Fu
   run_phase<false, G, 3, DEPTH>(p.down, none, p.ld2, p.inter, static_cast<int64_t>(p.h), p.h, p.d, p.y, p.ldy, ntok[0],
                                 ntok[1], s_tok, s_part, [&]() -> bool {
                                   __syncthreads();
+                                  stamp(3);           // first down-projection weights requested, before the wait
                                   if (threadIdx.x == 0) {
                                     __threadfence();
                                     unsigned long long* bar = &g_fused_barrier[p.slot];
@@ -358,8 +372,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_fused_kernel(const Fu
                                     }
                                   }
                                   __syncthreads();
+                                  stamp(4);           // the whole grid has finished gate/up
                                   return s_ok != 0;
                                 });
+  stamp(5);          // down projection done in this CTA
 }
 
 }  // namespace ffnk
@@ -367,6 +383,22 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_fused_kernel(const Fu
 using namespace ffnk;
 
 extern "C" int ffnk_decode_max_tokens(void) { return kDecodeTableTokens; }
+
+// Tile-table entry: does a forward of M tokens take this kernel?  Both paths stream the weights once; this
+// one adds the token rows that every CTA re-reads from L2 for each of its units (as many bytes as the
+// weights at 16 tokens per modality), the GEMM path adds about 25 us of fixed cost (routing, permutation
+// and two GEMM launches with their pipeline fill).  Fitted to measurements with both modalities present
+// (a = microseconds the weights take at 3.9 TB/s):
+//     decode(M) = (a + 6 us) * (1 + (M - 8) / 60),   gemm = 1.114 * a + 25 us
+// d=1024/h=2816 (a = 8.9): decode 14.9 us at 8 tokens, 28.7 at 64, 35.4 at 96; GEMM path 37: break-even
+// near 88.  d=4096/h=11008 (a = 139): decode 0.142 ms at 8 tokens, 0.292 at 64; GEMM path 0.154 at 96:
+// break-even near 22 tokens.
+extern "C" int ffnk_ffn_takes_decode(int64_t M, int64_t d, int64_t h) {
+  if (M < 1 || M > kDecodeTableTokens || d < 8 || h < 8) return 0;
+  const double a = 12.0 * static_cast<double>(d) * static_cast<double>(h) / 3.9e6;
+  const double limit = 8.0 + 60.0 * (0.114 * a + 19.0) / (a + 6.0);
+  return static_cast<double>(M) <= limit ? 1 : 0;
+}
 extern "C" int ffnk_decode_capacity(void) { return kFusedMaxTokens; }
 
 extern "C" int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
@@ -407,6 +439,7 @@ extern "C" int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const
   p.d = static_cast<int>(d);
   p.h = static_cast<int>(h);
   p.status = status;
+  p.prof = debug_profile_buffer();
   static unsigned launch_seq = 0;   // successive launches take successive barrier slots
   p.slot = static_cast<int>(__atomic_fetch_add(&launch_seq, 1u, __ATOMIC_RELAXED) % kFusedBarrierSlots);
 

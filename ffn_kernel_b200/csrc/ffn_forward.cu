@@ -69,7 +69,7 @@ extern "C" int ffnk_ffn_forward(const void* x, int64_t ldx, const void* w1, cons
   char* ws = static_cast<char*>(workspace);
 
   const bool k_major = w13_stride_k == 1 && w2_stride_k == 1;
-  if (allow_decode && M <= ffnk_decode_max_tokens() && k_major)
+  if (allow_decode && k_major && ffnk_ffn_takes_decode(M, d, h))
     return ffnk_ffn_decode(x, ldx, w1, w2, w3, u1, u2, u3, w13_stride_k, w13_stride_n, w2_stride_k, w2_stride_n, mask,
                            ws + w.inter, y, ldy, M, d, h, status, stream);
 

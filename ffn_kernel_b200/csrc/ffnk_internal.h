@@ -46,6 +46,9 @@ struct TuneOverrides {
 };
 TuneOverrides& tune_overrides();
 
+// Diagnostics buffer installed by ffnk_debug_profile_buffer (null when off): 8 int64 per CTA.
+long long* debug_profile_buffer();
+
 // permute_rows with an optional device-side gate: with only_if_scattered = T > 0 the kernel returns at
 // once unless the mask's runs of same-modality tokens average fewer than T rows.
 int permute_rows_launch(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out, int64_t ldo,

@@ -1551,6 +1551,7 @@ static int max_run_rows() {
 }
 
 static long long* g_prof_buffer = nullptr;
+long long* debug_profile_buffer() { return g_prof_buffer; }
 static int g_sm_margin = 0;   // SMs the persistent GEMM grids leave free (for a concurrent collective)
 
 static int usable_sms(const DeviceInfo& dev) {

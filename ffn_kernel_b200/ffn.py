@@ -57,7 +57,13 @@ def permute_rows_first(M: int, d: int, h: int) -> bool:
 
 
 def decode_max_tokens() -> int:
+    """Largest token count the tile table ever sends to the one-launch decode kernel."""
     return int(lib().ffnk_decode_max_tokens())
+
+
+def takes_decode(M: int, d: int, h: int) -> bool:
+    """Tile-table entry of the library: does a forward of this shape (K-major weights) take the decode kernel?"""
+    return bool(lib().ffnk_ffn_takes_decode(M, d, h))
 
 
 def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = None,
@@ -97,7 +103,7 @@ def _bf16_ffn_fused_forward(x, w1, w2, w3, u1, u2, u3, mask, rt: Route | None = 
             maybe_check(dev)
             return y
         # step by step (an observer wants the phase boundaries, or the caller brings routing lists)
-        if (allow_decode and rt is None and M <= decode_max_tokens() and w1.stride(0) == 1
+        if (allow_decode and rt is None and takes_decode(M, d, h) and w1.stride(0) == 1
                 and w2.stride(0) == 1):
             if mask.dim() != 1 or mask.shape[0] != M or mask.device != dev:
                 raise RuntimeError(f"mask must have shape [{M}] on {dev}")

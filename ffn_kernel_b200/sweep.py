@@ -57,6 +57,7 @@ def main():
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--mask", default="span")
     ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--decode", action="store_true", help="once: let small token counts take the decode kernel")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
@@ -140,7 +141,7 @@ def main():
         c = ffn_case(M, d, h, seed=0, mask=edge_mask(M, a.mask, 0)).to(dev)
         if a.what == "once":          # a couple of plain forward passes: the command ncu captures
             for _ in range(2):
-                _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)
+                _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=a.decode)
             torch.cuda.synchronize()
             check_status()
             return

@@ -229,11 +229,14 @@ int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int64_t block_
  * streams each present modality's weights once with 128-bit loads (the down-projection rows prefetched
  * into L2 while gate/up runs), with a bounded grid-wide wait between the two phases.  Same contract as
  * MaskedFFN.forward (ffn_kernel/ops.py:28-32).  inter: scratch bf16 [M, h].  K-major weights only.
- * Accepts M <= ffnk_decode_capacity() (127); ffnk_decode_max_tokens() (80) is the tile table's threshold:
- * up to it ffnk_ffn_forward takes this path, beyond it the GEMM path is faster.
+ * Accepts M <= ffnk_decode_capacity() (127).  ffnk_ffn_takes_decode(M, d, h) is the tile table's entry:
+ * whether ffnk_ffn_forward sends this shape here (never beyond ffnk_decode_max_tokens() = 80 tokens;
+ * wide FFNs switch to the GEMM path earlier, d=4096/h=11008 at 22 tokens, because every CTA re-reads
+ * the token rows for each of its row blocks).
  * ------------------------------------------------------------------------------------- */
 int ffnk_decode_max_tokens(void);
 int ffnk_decode_capacity(void);
+int ffnk_ffn_takes_decode(int64_t M, int64_t d, int64_t h);
 int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, const void* w3, const void* u1,
                     const void* u2, const void* u3, int64_t w13_stride_k, int64_t w13_stride_n, int64_t w2_stride_k,
                     int64_t w2_stride_n, const void* mask, void* inter, void* y, int64_t ldy, int64_t M, int64_t d,
@@ -242,7 +245,7 @@ int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, 
 /* ---------------------------------------------------------------------------------------
  * The whole MaskedFFN forward in one call (MaskedFFN.forward, ffn_kernel/ops.py:28-32):
  * routing, optional row permutation, gate/up, down -- or the decode kernel when
- * allow_decode != 0, M <= ffnk_decode_max_tokens() and the weights are K-major.
+ * allow_decode != 0, ffnk_ffn_takes_decode(M, d, h) and the weights are K-major.
  * workspace: ffnk_ffn_workspace_bytes(M, d, h) bytes of device memory, 256-byte aligned, owned by
  * the caller and reusable as soon as the stream has passed this call; too small a workspace
  * returns FFNK_ERR_CAPACITY.  ffnk_ffn_permute_first() tells whether the tile table copies x
@@ -299,7 +302,9 @@ int ffnk_set_sm_margin(int sms);
  * is non-null, the CTA-pair GEMM kernels launched afterwards store per-CTA cycle counters in it:
  * [0] MMA-issuer total, [1] its wait for operands, [2] its wait for a free accumulator,
  * [3] producer wait for a free stage, [4] producer total, [5] epilogue wait for an accumulator,
- * [6] epilogue total, [7] tiles.  Pass null to switch it off (the default).  Process-wide. */
+ * [6] epilogue total, [7] tiles.  The decode kernel stores cycle stamps since its start instead: [0] tokens
+ * counted, [1] first gate/up weights requested, [2] gate/up done, [3] first down weights requested,
+ * [4] grid-wide wait passed, [5] down projection done.  Pass null to switch it off (the default).  Process-wide. */
 int ffnk_debug_profile_buffer(void* buffer);
 
 /* Diagnostics: replaces one entry of the compiled-in tile table so that a choice can be timed against its
