@@ -180,9 +180,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// sigmoid(x) = 0.5 + 0.5 * tanh(0.5 x): one special-function instruction instead of an exponential and a
+// reciprocal (the epilogues of short-K tiles are bound by that unit); tanh.approx is good to 2^-11
+// relative, a quarter of a bf16 rounding step.
+__device__ __forceinline__ float sigmoid_fast(float x) { return fmaf(0.5f, tanh_approx(0.5f * x), 0.5f); }
+
 __device__ __forceinline__ float silu_mul(float t1, float t3) {
-  // t1 * sigmoid(t1) * t3 (ffn_kernel/ffn.py:107), in fp32
-  return t1 * __frcp_rn(1.0f + __expf(-t1)) * t3;
+  // t1 * sigmoid(t1) * t3 (ffn_kernel/ffn.py:107), in fp32: with h = t1 / 2, t1 * sigmoid(t1) = h + h * tanh(h)
+  const float h = 0.5f * t1;
+  return fmaf(h, tanh_approx(h), h) * t3;
 }
 
 
@@ -344,7 +355,7 @@ __device__ __forceinline__ void epilogue_dswiglu_staged(uint32_t taddr, const Ge
 #pragma unroll
     for (int e = 0; e < 32; ++e) {
       const float dh = __uint_as_float(acc[e]);
-      const float sg = __frcp_rn(1.0f + __expf(-t1[e]));
+      const float sg = sigmoid_fast(t1[e]);
       const float d1 = dh * t3[e] * sg * (1.0f + t1[e] * (1.0f - sg));
       t3[e] = dh * t1[e] * sg;     // d3
       t1[e] = d1;
