@@ -56,8 +56,13 @@ __device__ __forceinline__ ThreadTokens load_thread_tokens(const uint8_t* __rest
   }
   ThreadTokens t;
   t.bits = 0;
+  // four mask bytes -> four bits: the high bit of every non-zero byte, then one multiply that lines the
+  // bits of positions 0, 8, 16, 24 up at 24..27 (no two partial products share a bit position)
 #pragma unroll
-  for (int i = 0; i < kRoutePerThread; ++i) t.bits |= (((w[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0 ? 1u : 0u) << i;
+  for (int i = 0; i < kRoutePerThread / 4; ++i) {
+    const uint32_t nz = (((w[i] & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | w[i]) & 0x80808080u;
+    t.bits |= ((((nz >> 7) * 0x01020408u) >> 24) & 0xFu) << (4 * i);
+  }
   t.valid = valid;
   t.nruns = 0;
   if (valid > 0) {
@@ -95,7 +100,8 @@ __device__ __forceinline__ int block_exclusive_scan(int nv, int* s_warp, int* ti
 // The warp goes through its 32 threads' token groups one after the other, lane l taking token l of
 // the group: the lanes of one modality then write consecutive words (no bank conflicts; a thread
 // writing its own 32 tokens one by one puts the lanes 16 words apart, a 16-way conflict per store).
-__device__ __forceinline__ void compact_tile(int* s_list, int tile, uint32_t bits, int ev, int valid, int tile_v) {
+// s_v / s_t: where the tile's visual and text lists start in shared memory.
+__device__ __forceinline__ void compact_tile(int* s_v, int* s_t, int tile, uint32_t bits, int ev, int valid) {
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const uint32_t below = (1u << lane) - 1u;
@@ -108,8 +114,8 @@ __device__ __forceinline__ void compact_tile(int* s_list, int tile, uint32_t bit
       const int tid_r = (tid & ~31) + r;
       const int tok = tile * kRouteTile + tid_r * kRoutePerThread + lane;
       const int before = __popc(b & below);
-      if ((b >> lane) & 1u) s_list[ev_r + before] = tok;
-      else s_list[tile_v + (tid_r * kRoutePerThread - ev_r) + (lane - before)] = tok;
+      if ((b >> lane) & 1u) s_v[ev_r + before] = tok;
+      else s_t[(tid_r * kRoutePerThread - ev_r) + (lane - before)] = tok;
     }
   }
 }
@@ -206,7 +212,7 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
     }
   }
 
-  compact_tile(s_list, tile, bits, ev, valid, tile_v);
+  compact_tile(s_list, s_list + tile_v, tile, bits, ev, valid);
   __syncthreads();
   if (!s_ok) return;
   const int pre_v = s_excl;
@@ -291,10 +297,32 @@ __global__ void __launch_bounds__(kRouteThreads) route_count_kernel(const uint8_
   }
 }
 
+// One list of a tile, shared memory -> global memory.  The list was laid out in shared memory with the
+// same alignment (modulo four elements) as its destination, so everything between the first and the
+// last 16-byte boundary leaves as ONE bulk copy issued by a single thread; at most three elements at
+// either end are stored one by one.  `dst` and `src` address element 0 of the list.  `t0`: first of the
+// 96 threads that do the work (a different warp triple per list, so the two lists of a tile go out side
+// by side).
+__device__ __forceinline__ void store_list_bulk(int* dst, const int* src, int n, int t0) {
+  const int head = min(n, static_cast<int>((4u - ((reinterpret_cast<uintptr_t>(dst) >> 2) & 3u)) & 3u));
+  const int mid = (n - head) & ~3;
+  const int tid = static_cast<int>(threadIdx.x) - t0;
+  if (tid >= 0 && tid < head) dst[tid] = src[tid];
+  else if (tid >= 32 && tid < 32 + (n - head - mid)) dst[head + mid + tid - 32] = src[head + mid + tid - 32];
+  if (tid == 64 && mid > 0) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the list was written by ordinary stores
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + head),
+                 "r"(smem_u32(src + head)), "r"(mid * 4)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory may be released
+  }
+}
+
 __global__ void __launch_bounds__(kRouteThreads) route_scatter_kernel(const uint8_t* __restrict__ mask, int M, int cap,
                                                                       int* __restrict__ perm,
                                                                       const uint32_t* __restrict__ ws) {
-  __shared__ int s_list[kRouteTile];
+  __shared__ __align__(16) int s_list[kRouteTile + 16];
   __shared__ int s_warp[kRouteThreads / 32];
   const int tid = threadIdx.x;
   const int tile = blockIdx.x;
@@ -303,12 +331,15 @@ __global__ void __launch_bounds__(kRouteThreads) route_scatter_kernel(const uint
   const int ev = block_exclusive_scan(__popc(tt.bits), s_warp, &tile_v);
   const int tile_len = min(kRouteTile, M - tile * kRouteTile);
   const int tile_t = tile_len - tile_v;
-  compact_tile(s_list, tile, tt.bits, ev, tt.valid, tile_v);
-  __syncthreads();
   const int pre_v = static_cast<int>(ws[1 + tile]);
   const int pre_t = tile * kRouteTile - pre_v;
-  for (int i = tid; i < tile_v; i += kRouteThreads) perm[pre_v + i] = s_list[i];
-  for (int i = tid; i < tile_t; i += kRouteThreads) perm[cap + pre_t + i] = s_list[tile_v + i];
+  // both lists sit in shared memory at the alignment (mod 4 elements) of their places in perm
+  int* s_v = s_list + (pre_v & 3);
+  int* s_t = s_list + ((((pre_v & 3) + tile_v + 3) & ~3) + ((cap + pre_t) & 3));
+  compact_tile(s_v, s_t, tile, tt.bits, ev, tt.valid);
+  __syncthreads();
+  store_list_bulk(perm + pre_v, s_v, tile_v, 0);
+  store_list_bulk(perm + cap + pre_t, s_t, tile_t, 128);
 }
 
 __global__ void route_empty_kernel(int* counts, int cap) {
