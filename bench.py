@@ -506,6 +506,11 @@ def run_ours(args):
             "fused_broadcast": (lambda xi=x, mi=mask: tp.masked_ffn_tp_fused(xi, *w_tp, mi, blocks), 7,
                                 "down projection stores partial rows into their owner's memory over NVLink; own "
                                 "barrier kernel; owner sums in fp32 and stores the rows into every rank's y; barrier"),
+            "fused_broadcast_2col": (lambda xi=x, mi=mask: tp.masked_ffn_tp_fused(xi, *w_tp, mi, blocks, col_chunks=2), 9,
+                                     "the same with the down projection in two column ranges: barrier, sum and "
+                                     "broadcast of a range run on a side stream under the next range's GEMM"),
+            "fused_broadcast_4col": (lambda xi=x, mi=mask: tp.masked_ffn_tp_fused(xi, *w_tp, mi, blocks, col_chunks=4), 15,
+                                     "the same in four column ranges"),
             "fused_broadcast_2chunks": (lambda xi=x, mi=mask: tp.masked_ffn_tp_fused(xi, *w_tp, mi, blocks, chunks=2),
                                         13, "the same in two token chunks: barrier, sum and broadcast of a chunk "
                                             "run on a side stream under the next chunk's GEMMs"),
@@ -861,6 +866,16 @@ def c3_token_sharded(b: Bench) -> dict:
     out["with_overlapped_grad_allreduce_ms"] = b.time_steps(step_overlapped, n, 3)
     out["allreduce_exposed_ms"] = out["with_overlapped_grad_allreduce_ms"] - ms
     out["allreduce_hidden_ms"] = out["with_grad_allreduce_ms"] - out["with_overlapped_grad_allreduce_ms"]
+    # the same with the bf16 gradients all-reduced in place (no fp32 bucket)
+    sync_bf16 = tp.GradientSync(reduce_dtype=None)
+
+    def step_overlapped_bf16():
+        xs.grad = wv.grad = wt.grad = None
+        with sync_bf16:
+            MaskedLinear.apply(xs, wv.T, wt.T, ms_).backward(gs)
+    out["with_overlapped_bf16_allreduce_ms"] = b.time_steps(step_overlapped_bf16, n, 3)
+    step_overlapped_bf16()
+    gv16, gt16 = wv.grad.clone(), wt.grad.clone()
 
     # summed partial gradients against the gradient of the whole batch on one GPU
     step_overlapped()
@@ -872,8 +887,10 @@ def c3_token_sharded(b: Bench) -> dict:
     check_status()
     err = max(rel_err(gv_sum.T, gv_full), rel_err(gt_sum.T, gt_full))
     out["grad_allreduce_err"] = b.max_over_ranks(err)
+    out["grad_allreduce_bf16_err"] = b.max_over_ranks(max(rel_err(gv16.T, gv_full), rel_err(gt16.T, gt_full)))
     out["dx_rows_vs_single_gpu"] = b.max_over_ranks(rel_err(dx_shard, dx_full[rows]))
-    if not (out["grad_allreduce_err"] < PARITY_TOL and out["dx_rows_vs_single_gpu"] < PARITY_TOL):
+    if not (out["grad_allreduce_err"] < PARITY_TOL and out["dx_rows_vs_single_gpu"] < PARITY_TOL
+            and out["grad_allreduce_bf16_err"] < 2 * PARITY_TOL):
         out["parity_failure"] = (f"c3_dp: grad_allreduce_err {out['grad_allreduce_err']:.3e}, "
                                  f"dx {out['dx_rows_vs_single_gpu']:.3e}")
     return out

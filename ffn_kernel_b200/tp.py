@@ -170,7 +170,9 @@ class GradientSync:
     the NCCL all-reduce on a side stream; the dx GEMM is launched on the compute stream beside it, leaving
     ``sm_margin`` SMs to the collective's kernels; before the backward returns, the compute stream is made
     to wait for the reduced gradients (written back in place), so autograd only ever sees the sums.  What
-    the dx GEMM does not cover of the all-reduce is exposed.  The reference has no distributed path
+    the dx GEMM does not cover of the all-reduce is exposed.  ``reduce_dtype=torch.float32`` (default) sums
+    over ranks in fp32 through one packed bucket; ``reduce_dtype=None`` all-reduces the bf16 gradients in
+    place (no packing pass, half the bytes, bf16 additions).  The reference has no distributed path
     (``ffn_kernel/linear.py:455-496`` is the single-device partial)."""
 
     def __init__(self, group=None, average: bool = False, sm_margin: int = 16, reduce_dtype=torch.float32):
@@ -206,16 +208,25 @@ class GradientSync:
             # gradients are packed in the order of their storage (a weight gradient carries its weight's
             # strides, usually the transposed view of [out, in] storage): a flat view, not a transposing copy
             views = [_storage_order_view(g) for g in grads]
-            flat = torch.cat([v.reshape(-1).to(self.reduce_dtype) for v in views])
-            work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-            work.wait()                                 # stream-level: the side stream waits, the host does not
-            if self.average:
-                flat /= world
-            off = 0
-            for v in views:
-                n = v.numel()
-                v.copy_(flat[off:off + n].view(v.shape))
-                off += n
+            if self.reduce_dtype is None:
+                # in place, in the gradients' own dtype: no packing pass, half the bytes of an fp32 bucket
+                flat = None
+                for v in views:
+                    work = dist.all_reduce(v, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+                    work.wait()
+                    if self.average:
+                        v /= world
+            else:
+                flat = torch.cat([v.reshape(-1).to(self.reduce_dtype) for v in views])
+                work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+                work.wait()                             # stream-level: the side stream waits, the host does not
+                if self.average:
+                    flat /= world
+                off = 0
+                for v in views:
+                    n = v.numel()
+                    v.copy_(flat[off:off + n].view(v.shape))
+                    off += n
             done = torch.cuda.Event()
             done.record(side)
         lib().ffnk_set_sm_margin(self.sm_margin)        # the dx GEMM launched next leaves SMs to the collective
@@ -223,7 +234,8 @@ class GradientSync:
         def finish(flat=flat, grads=grads):
             lib().ffnk_set_sm_margin(0)
             main.wait_event(done)
-            flat.record_stream(main)
+            if flat is not None:
+                flat.record_stream(main)
         return finish
 
 
@@ -300,6 +312,7 @@ class PeerBlocks:
             y, yptrs = mapped(max(M, 1) * d, torch.bfloat16)
             self.outs.append(y.view(max(M, 1), d))
             self.out_ptrs.append((ctypes.c_void_p * self.world)(*yptrs))
+            self._out_ptr_values = getattr(self, "_out_ptr_values", []) + [yptrs]
         self.pointers = [(ctypes.c_void_p * self.world)(*p) for p in self.buffer_ptrs]
         flags, fptrs = mapped(64, torch.int32)
         flags.zero_()
@@ -319,14 +332,27 @@ class PeerBlocks:
         self._turn = (i + 1) % len(self.buffers)
         return i, self.buffers[i], self.pointers[i], self.outs[i], self.out_ptrs[i]
 
-    def block_pointers(self, i: int, row_offset: int):
-        """Peer pointers of block buffer ``i`` advanced by ``row_offset`` rows (one chunk's region)."""
+    def block_pointers(self, i: int, row_offset: int, col: int = 0):
+        """Peer pointers of block buffer ``i`` advanced by ``row_offset`` rows (one chunk's region) and
+        ``col`` columns (one column range of the output)."""
         import ctypes
-        key = (i, row_offset)
+        key = ("b", i, row_offset, col)
         p = self._ptr_cache.get(key)
         if p is None:
-            off = row_offset * self.d * 2
+            off = (row_offset * self.d + col) * 2
             p = (ctypes.c_void_p * self.world)(*[q + off for q in self.buffer_ptrs[i]])
+            self._ptr_cache[key] = p
+        return p
+
+    def out_pointers(self, i: int, col: int = 0):
+        """Peer pointers of output matrix ``i`` advanced by ``col`` columns."""
+        import ctypes
+        if col == 0:
+            return self.out_ptrs[i]
+        key = ("o", i, col)
+        p = self._ptr_cache.get(key)
+        if p is None:
+            p = (ctypes.c_void_p * self.world)(*[int(q) + col * 2 for q in self._out_ptr_values[i]])
             self._ptr_cache[key] = p
         return p
 
@@ -346,7 +372,8 @@ class PeerBlocks:
         return peer_owned_rows(self.M, self.rank, self.world)
 
 
-def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gather: bool = True, chunks: int = 1):
+def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gather: bool = True, chunks: int = 1,
+                        col_chunks: int = 1):
     """Tensor-parallel MaskedFFN forward whose communication is done by this library's own kernels
     over NVLink peer memory; no collective library call is on the path.
 
@@ -361,6 +388,10 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
     ``(rows, y[rows])`` with ``rows = blocks.owned_rows()`` and skips the broadcast.
     ``chunks > 1`` (``gather=True`` only) splits the tokens into that many row ranges; the barrier,
     sum and broadcast of one chunk run on a side stream under the GEMMs of the next.
+    ``col_chunks > 1`` (``gather=True``, ``chunks == 1``) splits only the down projection, by output
+    columns: gate/up runs once over all tokens, and the barrier, sum and broadcast of one column range
+    run on a side stream under the down projection of the next, so that half of the broadcast crosses
+    the link while the GEMM still computes.
     The weights are this rank's shards (``shard_ffn_weights``); ``x`` and ``mask`` are replicated."""
     from ._lib import check, lib
     from .ffn import _phase, permute_rows_first
@@ -378,6 +409,7 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
     chunks = max(1, min(int(chunks), blocks.MAX_CHUNKS, max(1, M)))
     if chunks > 1 and not gather:
         raise ValueError("chunks > 1 needs gather=True (owned rows are interleaved by chunk)")
+    col_chunks = max(1, min(int(col_chunks), 8, d // 256)) if (gather and chunks == 1 and d % 8 == 0) else 1
     dev = x.device
     L = lib()
     world, rank = blocks.world, blocks.rank
@@ -386,8 +418,8 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
         main = torch.cuda.current_stream(dev)
         turn, buf, _, y, y_ptrs = blocks.next()
 
-        def compute_chunk(tok: slice, rows_c: int, block_ptrs):
-            """route, (permute,) gate/up and the peer-storing down projection of one token range"""
+        def gate_up(tok: slice):
+            """route, (permute,) gate/up of one token range -> (routing lists, routed intermediate)"""
             Mc = tok.stop - tok.start
             sp = stream_ptr(dev)
             xc, mc = x[tok], mask[tok]
@@ -408,12 +440,23 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
                 w1.stride(0), w1.stride(1), rt.perm.data_ptr(), rt.counts.data_ptr(), inter.data_ptr(),
                 inter.stride(0), routed_in, 1, Mc, d, h, st, sp))
             _phase("down")
+            return rt, inter
+
+        def down_to_peers(rt, inter, Mc: int, rows_c: int, block_ptrs, col0: int = 0, ncols: int = d):
+            """the peer-storing down projection of output columns [col0, col0 + ncols)"""
+            wv, wu = w2[:, col0:col0 + ncols], u2[:, col0:col0 + ncols]
             check("ffnk_ffn_down_to_peers", L.ffnk_ffn_down_to_peers(
-                inter.data_ptr(), inter.stride(0), w2.data_ptr(), u2.data_ptr(), w2.stride(0), w2.stride(1),
-                rt.perm.data_ptr(), rt.counts.data_ptr(), block_ptrs, world, rank, rows_c, d, Mc, d, h, st, sp))
+                inter.data_ptr(), inter.stride(0), wv.data_ptr(), wu.data_ptr(), wv.stride(0), wv.stride(1),
+                rt.perm.data_ptr(), rt.counts.data_ptr(), block_ptrs, world, rank, rows_c, d, Mc, ncols, h, st,
+                stream_ptr(dev)))
+
+        def compute_chunk(tok: slice, rows_c: int, block_ptrs):
+            rt, inter = gate_up(tok)
+            down_to_peers(rt, inter, tok.stop - tok.start, rows_c, block_ptrs)
             _phase("end")
 
-        def sum_chunk(tok: slice, rows_c: int, region_row0: int, to_peers: bool, own=None, max_ctas: int = 0):
+        def sum_chunk(tok: slice, rows_c: int, region_row0: int, to_peers: bool, own=None, max_ctas: int = 0,
+                      col0: int = 0, ncols: int = d):
             """this rank's rows of one token range: fp32 sum of the world partials, to every rank or locally"""
             Mc = tok.stop - tok.start
             n_own = max(0, min(rows_c, Mc - rank * rows_c))
@@ -423,7 +466,8 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
             sp = stream_ptr(dev)
             if to_peers:
                 check("ffnk_sum_row_blocks_to_peers", L.ffnk_sum_row_blocks_to_peers(
-                    src.data_ptr(), world, rows_c, n_own, d, d, y_ptrs, world, tok.start + rank * rows_c, d, max_ctas, sp))
+                    src.data_ptr() + col0 * 2, world, rows_c, n_own, ncols, d, blocks.out_pointers(turn, col0), world,
+                    tok.start + rank * rows_c, d, max_ctas, sp))
             else:
                 # blocks are rows_c rows apart; only the first n_own rows of each exist
                 check("ffnk_sum_row_blocks", L.ffnk_sum_row_blocks(src.data_ptr(), world, rows_c, d, d, own.data_ptr(), d, sp))
@@ -433,7 +477,7 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
                 return y[:0]
             return blocks.owned_rows(), torch.empty((0, d), device=dev, dtype=torch.bfloat16)
 
-        if chunks == 1:
+        if chunks == 1 and col_chunks == 1:
             tok, rows_c = slice(0, M), blocks.rows
             compute_chunk(tok, rows_c, blocks.block_pointers(turn, 0))
             blocks.barrier()
@@ -449,6 +493,33 @@ def masked_ffn_tp_fused(x, w1, w2, w3, u1, u2, u3, mask, blocks: PeerBlocks, gat
             return y[:M]
 
         side = blocks._side
+        if chunks == 1:
+            # one gate/up over all tokens; the down projection in column ranges (multiples of 256 columns),
+            # each range's barrier, sum and broadcast on the side stream under the next range's GEMM
+            tok, rows_c = slice(0, M), blocks.rows
+            rt, inter = gate_up(tok)
+            step = -(-(d // 256) // col_chunks) * 256
+            col0 = 0
+            while col0 < d:
+                ncols = min(step, d - col0)
+                down_to_peers(rt, inter, M, rows_c, blocks.block_pointers(turn, 0, col0), col0, ncols)
+                ev = torch.cuda.Event()
+                ev.record(main)
+                side.wait_event(ev)
+                with torch.cuda.stream(side):
+                    blocks.barrier()
+                    sum_chunk(tok, rows_c, 0, True, max_ctas=0 if col0 + ncols >= d else 148, col0=col0, ncols=ncols)
+                col0 += ncols
+            _phase("end")
+            with torch.cuda.stream(side):
+                blocks.barrier()
+                done = torch.cuda.Event()
+                done.record(side)
+            main.wait_event(done)
+            inter.record_stream(main)
+            maybe_check(dev)
+            return y[:M]
+
         region = 0
         for c in range(chunks):
             tok = row_shard(M, c, chunks)

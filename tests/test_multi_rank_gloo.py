@@ -118,3 +118,43 @@ def test_weight_shards_are_views():
     assert sh[0].shape == (64, 64) and sh[1].shape == (64, 64)
     assert sh[0].untyped_storage().data_ptr() == c.w1.untyped_storage().data_ptr()
     assert sh[1].untyped_storage().data_ptr() == c.w2.untyped_storage().data_ptr()
+
+
+def test_storage_order_view_of_weight_gradients():
+    # a weight gradient carries its weight's strides (the transposed view of [out, in] storage): packing
+    # it for the all-reduce must be a flat view of the memory, not a transposing copy
+    g = torch.arange(12.0).reshape(3, 4).T                     # logical [4, 3], memory order [3, 4]
+    v = tp._storage_order_view(g)
+    assert v.is_contiguous() and v.data_ptr() == g.data_ptr() and v.shape == (3, 4)
+    assert v.reshape(-1).data_ptr() == g.data_ptr()            # flattening is free
+    c = torch.zeros(4, 3)
+    assert tp._storage_order_view(c) is c
+
+
+def test_gradient_sync_hook_is_installed_and_removed():
+    from ffn_kernel_b200 import linear
+    assert linear.GRAD_HOOK is None
+    with tp.GradientSync() as outer:
+        assert linear.GRAD_HOOK == outer._hook
+        with tp.GradientSync(reduce_dtype=None) as inner:
+            assert linear.GRAD_HOOK == inner._hook
+        assert linear.GRAD_HOOK == outer._hook
+    assert linear.GRAD_HOOK is None
+    # without a process group (one rank) the hook starts nothing and hands back a no-op
+    done = tp.GradientSync()._hook(torch.zeros(2, 2))
+    done()
+
+
+def test_chunk_regions_fit_the_block_buffers():
+    # chunked calls place each chunk's world * ceil(Mc / world) block rows one after the other; the buffers
+    # are allocated with MAX_CHUNKS spare rows per block
+    for M in (1, 9, 1000, 16384, 16385):
+        for world in (2, 3, 8):
+            rows = tp.peer_block_rows(M, world)
+            total = world * (rows + tp.PeerBlocks.MAX_CHUNKS)
+            for chunks in range(1, tp.PeerBlocks.MAX_CHUNKS + 1):
+                used = 0
+                for c in range(min(chunks, M)):
+                    tok = tp.row_shard(M, c, min(chunks, M))
+                    used += world * tp.peer_block_rows(tok.stop - tok.start, world)
+                assert used <= total, (M, world, chunks)

@@ -62,6 +62,7 @@ def main():
     rows, y_own = tp.masked_ffn_tp_fused(x, *shards, mask, blocks, gather=False)
     y_nccl = tp.masked_ffn_tp(x, *shards, mask)
     y_chunked = {c: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, chunks=c).clone() for c in (2, 3)}
+    y_chunked.update({f"col{c}": tp.masked_ffn_tp_fused(x, *shards, mask, blocks, col_chunks=c).clone() for c in (2, 4)})
     torch.cuda.synchronize()
     check_status()
     out["fused_vs_nccl"] = float((y_fused.float() - y_nccl.float()).abs().max() / y_nccl.float().abs().max())
@@ -86,6 +87,8 @@ def main():
     if args.time:
         flops = 6.0 * args.tokens * args.dim * args.hidden
         for name, fn in (("fused_broadcast", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks)),
+                         ("fused_broadcast_2col", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, col_chunks=2)),
+                         ("fused_broadcast_4col", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, col_chunks=4)),
                          ("fused_broadcast_2chunks", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, chunks=2)),
                          ("fused_broadcast_4chunks", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, chunks=4)),
                          ("fused_row_sharded", lambda: tp.masked_ffn_tp_fused(x, *shards, mask, blocks, gather=False)),
