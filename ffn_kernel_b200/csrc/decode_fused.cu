@@ -1,5 +1,5 @@
 // Small-M (decode) MaskedFFN forward in ONE launch: both phases (gate/up with the SiLU(t1)*t3 epilogue, then
-// the down projection) of up to 127 tokens, judged against HBM bandwidth: every weight of each modality
+// the down projection) of up to 127 tokens, a kernel bound by HBM bandwidth: every weight of each modality
 // that has tokens is streamed exactly once (3*d*h bf16 per modality) by 128-bit loads.
 //
 // One persistent CTA per SM, 16 warps.  A work unit is 8 weight rows over the whole contraction

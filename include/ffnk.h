@@ -24,6 +24,9 @@
  *   - mask: one byte per token, non-zero = first weight set ("visual"), zero = second ("text")
  *     (ffn_kernel/linear.py:137-140).
  *   - Routing lists (`perm`, `counts`) are produced by ffnk_route() on the same stream.
+ *   - The GEMM entry points encode TMA tensor maps on the host through the driver, which needs the
+ *     device's primary context bound to the calling thread; the first such call on a thread binds it
+ *     (cudaFree(0)).  Make a thread's first call outside any stream capture; later calls can be captured.
  */
 #ifndef FFNK_H_
 #define FFNK_H_
@@ -225,10 +228,14 @@ int ffnk_sum_row_blocks_to_peers(const void* blocks, int nblocks, int64_t block_
                                  int max_ctas, void* stream);
 
 /* ---------------------------------------------------------------------------------------
- * Small-M (decode) MaskedFFN forward in one launch, judged against HBM bandwidth: one persistent kernel
+ * Small-M (decode) MaskedFFN forward in one launch, bound by HBM bandwidth: one persistent kernel
  * streams each present modality's weights once with 128-bit loads (the down-projection rows prefetched
  * into L2 while gate/up runs), with a bounded grid-wide wait between the two phases.  Same contract as
  * MaskedFFN.forward (ffn_kernel/ops.py:28-32).  inter: scratch bf16 [M, h].  K-major weights only.
+ * The grid-wide wait counts arrivals in one of 64 counters inside the library; successive launches take
+ * successive counters and a launch captured into a CUDA graph keeps the one it was captured with, so two
+ * launches that may run on the GPU at the same time must not be a multiple of 64 launches apart (launches
+ * on one stream never overlap; graphs that replay concurrently should be captured back to back).
  * Accepts M <= ffnk_decode_capacity() (127).  ffnk_ffn_takes_decode(M, d, h) is the tile table's entry:
  * whether ffnk_ffn_forward sends this shape here (never beyond ffnk_decode_max_tokens() = 80 tokens;
  * wide FFNs switch to the GEMM path earlier, d=4096/h=11008 at 22 tokens, because every CTA re-reads
