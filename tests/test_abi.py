@@ -46,6 +46,26 @@ def test_pure_host_functions(libffnk):
     assert b"null" in L.ffnk_status_string(-1)
 
 
+def test_decode_table_entry(libffnk):
+    # up to 80 tokens at the small FFN, fewer the wider the FFN, never beyond the kernel's capacity; monotone in M
+    L = libffnk
+    assert L.ffnk_decode_max_tokens() == 80 and L.ffnk_decode_capacity() == 127
+    for d, h, lo, hi in ((1024, 2816, 80, 80), (4096, 11008, 16, 32), (256, 520, 80, 80)):
+        takes = [bool(L.ffnk_ffn_takes_decode(M, d, h)) for M in range(0, 130)]
+        limit = max(M for M, t in enumerate(takes) if t)
+        assert lo <= limit <= hi, (d, h, limit)
+        assert not takes[0] and all(takes[1:limit + 1]) and not any(takes[limit + 1:])
+
+
+def test_tune_override_names(libffnk):
+    L = libffnk
+    for name in (b"pair", b"narrow", b"permute", b"epi_warps", b"group_m", b"wgrad_pair", b"max_run_rows",
+                 b"copy_threshold", b"verbose"):
+        assert L.ffnk_tune_override(name, -1) == 0
+    assert L.ffnk_tune_override(b"no_such_entry", 1) < 0
+    assert L.ffnk_tune_override(None, 1) < 0
+
+
 def test_argument_errors_are_reported_before_any_launch(libffnk):
     L = libffnk
     # null pointers
