@@ -846,7 +846,7 @@ def c3_token_sharded(b: Bench) -> dict:
     n = 10
     ms = b.time_steps(train_step, n, 3)
     out = {"ms_per_step": ms, "value": 6.0 * M * K * N / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "scaling": "strong",
-           "tokens_per_s": M / (ms * 1e-3), "steps": n,
+           "tokens_per_s": M / (ms * 1e-3), "steps": n, "launch": "eager",
            "what": f"MaskedLinear forward + backward, M={M}, K=N={K}, {M // world} rows per rank, no data-path "
                    "collective; max over ranks"}
 
@@ -893,6 +893,20 @@ def c3_token_sharded(b: Bench) -> dict:
             and out["grad_allreduce_bf16_err"] < 2 * PARITY_TOL):
         out["parity_failure"] = (f"c3_dp: grad_allreduce_err {out['grad_allreduce_err']:.3e}, "
                                  f"dx {out['dx_rows_vs_single_gpu']:.3e}")
+
+    # Last, the plain step replayed from a CUDA graph: at 8 GPUs a rank's 4096 rows are 0.35 ms of kernels, about
+    # what Python and autograd spend on one call, so the eager figure is host bound and moves with the host's load.
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            train_step()
+        gms = b.time_steps(graph.replay, n, 3)
+        out.update(eager_ms_per_step=ms, graph_ms_per_step=gms)
+        if gms < ms:      # host bound when launched eagerly: the replayed step is the device's time
+            out.update(ms_per_step=gms, launch="CUDA graph replay", value=6.0 * M * K * N / (gms * 1e-3) / 1e12,
+                       tokens_per_s=M / (gms * 1e-3))
+    except Exception as e:  # the capture is a convenience of the measurement, not part of the operator
+        out["graph_error"] = f"{type(e).__name__}: {e}"[:200]
     return out
 
 
