@@ -42,6 +42,19 @@ struct ThreadTokens {
   int nruns;
 };
 
+// 32 mask bytes (eight words) -> 32 bits.  Four bytes at a time: the high bit of every non-zero byte, then
+// one multiply that lines the bits of positions 0, 8, 16, 24 up at 24..27 (no two partial products share
+// a bit position).
+__device__ __forceinline__ uint32_t mask_words_to_bits(const uint32_t (&w)[kRoutePerThread / 4]) {
+  uint32_t bits = 0;
+#pragma unroll
+  for (int i = 0; i < kRoutePerThread / 4; ++i) {
+    const uint32_t nz = (((w[i] & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | w[i]) & 0x80808080u;
+    bits |= ((((nz >> 7) * 0x01020408u) >> 24) & 0xFu) << (4 * i);
+  }
+  return bits;
+}
+
 __device__ __forceinline__ ThreadTokens load_thread_tokens(const uint8_t* __restrict__ mask, int M, int base) {
   uint32_t w[kRoutePerThread / 4] = {};
   int valid = M - base;
@@ -52,17 +65,12 @@ __device__ __forceinline__ ThreadTokens load_thread_tokens(const uint8_t* __rest
     w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w;
     w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
   } else {
-    for (int i = 0; i < valid; ++i) w[i >> 2] |= static_cast<uint32_t>(mask[base + i]) << (8 * (i & 3));
+#pragma unroll    // fully unrolled: the words stay in registers
+    for (int i = 0; i < kRoutePerThread; ++i)
+      if (i < valid) w[i >> 2] |= static_cast<uint32_t>(mask[base + i]) << (8 * (i & 3));
   }
   ThreadTokens t;
-  t.bits = 0;
-  // four mask bytes -> four bits: the high bit of every non-zero byte, then one multiply that lines the
-  // bits of positions 0, 8, 16, 24 up at 24..27 (no two partial products share a bit position)
-#pragma unroll
-  for (int i = 0; i < kRoutePerThread / 4; ++i) {
-    const uint32_t nz = (((w[i] & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | w[i]) & 0x80808080u;
-    t.bits |= ((((nz >> 7) * 0x01020408u) >> 24) & 0xFu) << (4 * i);
-  }
+  t.bits = mask_words_to_bits(w);
   t.valid = valid;
   t.nruns = 0;
   if (valid > 0) {
@@ -96,26 +104,32 @@ __device__ __forceinline__ int block_exclusive_scan(int nv, int* s_warp, int* ti
   return warp_off + incl - nv;
 }
 
-// Compaction inside the tile: visual indices to s_list[0..tile_v), text to s_list[tile_v..tile_len).
-// The warp goes through its 32 threads' token groups one after the other, lane l taking token l of
-// the group: the lanes of one modality then write consecutive words (no bank conflicts; a thread
-// writing its own 32 tokens one by one puts the lanes 16 words apart, a 16-way conflict per store).
-// s_v / s_t: where the tile's visual and text lists start in shared memory.
+// Compaction inside the tile: visual indices to s_v[0..tile_v), text indices to s_t[0..tile_t), both
+// ascending.  Every thread walks its own 32 consecutive tokens and appends each index to its modality's
+// list (ev: visual tokens of the tile before this thread; valid: how many of the 32 tokens exist): six
+// instructions a token.  Neighbouring lanes write about 16 words apart, a few-way bank conflict per
+// store, which costs less than the three shuffles and two population counts per token group of a
+// conflict-free warp-transposed order (20 instructions per 32 tokens and lane: the scatter kernel was
+// bound by instruction issue, not by DRAM).
 __device__ __forceinline__ void compact_tile(int* s_v, int* s_t, int tile, uint32_t bits, int ev, int valid) {
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const uint32_t below = (1u << lane) - 1u;
-#pragma unroll 4
-  for (int r = 0; r < 32; ++r) {
-    const uint32_t b = __shfl_sync(0xFFFFFFFFu, bits, r);
-    const int ev_r = __shfl_sync(0xFFFFFFFFu, ev, r);
-    const int valid_r = __shfl_sync(0xFFFFFFFFu, valid, r);
-    if (lane < valid_r) {
-      const int tid_r = (tid & ~31) + r;
-      const int tok = tile * kRouteTile + tid_r * kRoutePerThread + lane;
-      const int before = __popc(b & below);
-      if ((b >> lane) & 1u) s_v[ev_r + before] = tok;
-      else s_t[(tid_r * kRoutePerThread - ev_r) + (lane - before)] = tok;
+  const int first = static_cast<int>(threadIdx.x) * kRoutePerThread;   // this thread's first token within the tile
+  int* pv = s_v + ev;
+  int* pt = s_t + (first - ev);
+  const int tok0 = tile * kRouteTile + first;
+  if (valid == kRoutePerThread) {
+#pragma unroll
+    for (int i = 0; i < kRoutePerThread; ++i) {
+      const bool vis = (bits >> i) & 1u;
+      *(vis ? pv : pt) = tok0 + i;
+      pv += vis ? 1 : 0;
+      pt += vis ? 0 : 1;
+    }
+  } else {
+    for (int i = 0; i < valid; ++i) {
+      const bool vis = (bits >> i) & 1u;
+      *(vis ? pv : pt) = tok0 + i;
+      pv += vis ? 1 : 0;
+      pt += vis ? 0 : 1;
     }
   }
 }
@@ -138,7 +152,6 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
   const int base = tile * kRouteTile + tid * kRoutePerThread;
   const ThreadTokens tt = load_thread_tokens(mask, M, base);
   const uint32_t bits = tt.bits;
-  const int valid = tt.valid;
   const int nv = __popc(bits);
   if (tid == 0) s_runs = 0;
   int tile_v = 0;
@@ -212,7 +225,7 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
     }
   }
 
-  compact_tile(s_list, s_list + tile_v, tile, bits, ev, valid);
+  compact_tile(s_list, s_list + tile_v, tile, bits, ev, tt.valid);
   __syncthreads();
   if (!s_ok) return;
   const int pre_v = s_excl;
@@ -245,48 +258,102 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const uint8_t* __r
 // the 5 bytes per token).  Here the first kernel counts (1 byte per token read) and its last block
 // to finish turns the per-tile counts into exclusive prefixes; the second kernel reads the mask
 // again and writes the lists (6 bytes per token in all).
-// ws: [0] run total, [1..tiles] per-tile visual count -> exclusive prefix, [tiles+1] finished tiles.
+// ws: [0] run total, [1..tiles] per-tile visual count -> exclusive prefix, [tiles+1] finished blocks of the count kernel.
 // -------------------------------------------------------------------------------------------
 constexpr int kLookBackMaxTiles = 128;
 
+constexpr int kCountTiles = 4;       // tiles per block of the count kernel: 128 mask bytes per thread in flight
+
 __global__ void __launch_bounds__(kRouteThreads) route_count_kernel(const uint8_t* __restrict__ mask, int M, int cap,
-                                                                    int* __restrict__ counts,
+                                                                    int num_tiles, int* __restrict__ counts,
                                                                     uint32_t* __restrict__ ws) {
+  __shared__ int s_cnt[kCountTiles][kRouteThreads / 32];
   __shared__ int s_warp[kRouteThreads / 32];
   __shared__ int s_runs, s_last;
-  const int tid = threadIdx.x;
-  const int tile = blockIdx.x;
-  const int num_tiles = gridDim.x;
-  const ThreadTokens tt = load_thread_tokens(mask, M, tile * kRouteTile + tid * kRoutePerThread);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile0 = blockIdx.x * kCountTiles;
   if (tid == 0) s_runs = 0;
-  int tile_v = 0;
-  block_exclusive_scan(__popc(tt.bits), s_warp, &tile_v);
+  uint32_t bits[kCountTiles];
+  int nruns = 0;
+  if (static_cast<int64_t>(tile0 + kCountTiles) * kRouteTile <= M && (reinterpret_cast<uintptr_t>(mask) & 15) == 0) {
+    // whole tiles: all eight 16-byte loads of the thread first (one byte per warp more: the token before
+    // the warp's first, for the run count), then the arithmetic
+    uint4 v[kCountTiles][2];
+    uint32_t prev_byte[kCountTiles];
+#pragma unroll
+    for (int j = 0; j < kCountTiles; ++j) {
+      const int base = (tile0 + j) * kRouteTile + tid * kRoutePerThread;
+      v[j][0] = *reinterpret_cast<const uint4*>(mask + base);
+      v[j][1] = *reinterpret_cast<const uint4*>(mask + base + 16);
+      prev_byte[j] = (lane == 0 && base > 0) ? mask[base - 1] : 0u;
+    }
+#pragma unroll
+    for (int j = 0; j < kCountTiles; ++j) {
+      const uint32_t w[8] = {v[j][0].x, v[j][0].y, v[j][0].z, v[j][0].w, v[j][1].x, v[j][1].y, v[j][1].z, v[j][1].w};
+      bits[j] = mask_words_to_bits(w);
+      // a run starts at every token whose modality differs from its predecessor's (token 0 always)
+      uint32_t prev = __shfl_up_sync(0xFFFFFFFFu, bits[j] >> 31, 1);
+      if (lane == 0) {
+        const int base = (tile0 + j) * kRouteTile + tid * kRoutePerThread;
+        prev = base > 0 ? (prev_byte[j] != 0 ? 1u : 0u) : ((bits[j] & 1u) ^ 1u);
+      }
+      nruns += __popc(bits[j] ^ ((bits[j] << 1) | prev));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kCountTiles; ++j) {
+      const ThreadTokens tt = load_thread_tokens(mask, M, (tile0 + j) * kRouteTile + tid * kRoutePerThread);
+      bits[j] = tt.bits;
+      nruns += tt.nruns;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kCountTiles; ++j) {
+    const int c = __reduce_add_sync(0xFFFFFFFFu, __popc(bits[j]));
+    if (lane == 0) s_cnt[j][warp] = c;
+  }
+  __syncthreads();                     // s_runs is zero, s_cnt is complete
   {
-    const int wr = __reduce_add_sync(0xFFFFFFFFu, tt.nruns);
-    if ((tid & 31) == 0 && wr) atomicAdd(&s_runs, wr);
+    const int wr = __reduce_add_sync(0xFFFFFFFFu, nruns);
+    if (lane == 0 && wr) atomicAdd(&s_runs, wr);
+  }
+  if (tid < kCountTiles && tile0 + tid < num_tiles) {
+    int c = 0;
+#pragma unroll
+    for (int i = 0; i < kRouteThreads / 32; ++i) c += s_cnt[tid][i];
+    ws[1 + tile0 + tid] = static_cast<uint32_t>(c);
+    __threadfence();
   }
   __syncthreads();
   if (tid == 0) {
-    ws[1 + tile] = static_cast<uint32_t>(tile_v);
     atomicAdd(&ws[0], static_cast<uint32_t>(s_runs));
     __threadfence();
-    s_last = atomicAdd(&ws[1 + num_tiles], 1u) == static_cast<uint32_t>(num_tiles - 1);
+    s_last = atomicAdd(&ws[1 + num_tiles], 1u) == gridDim.x - 1;
   }
   __syncthreads();
   if (!s_last) return;
-  // every other block has published its count: exclusive prefix over the tiles, in place
+  // every other block has published its counts: exclusive prefix over the tiles, in place; 2048 tiles a
+  // round, a thread's eight loads issued together (read around L1: other SMs wrote them)
   __threadfence();
-  volatile uint32_t* cnt = ws + 1;
-  const int per = (num_tiles + kRouteThreads - 1) / kRouteThreads;
-  const int lo = min(num_tiles, tid * per), hi = min(num_tiles, lo + per);
-  int sum = 0;
-  for (int i = lo; i < hi; ++i) sum += static_cast<int>(cnt[i]);
+  uint32_t* cnt = ws + 1;
   int total = 0;
-  int run = block_exclusive_scan(sum, s_warp, &total);
-  for (int i = lo; i < hi; ++i) {
-    const int c = static_cast<int>(cnt[i]);
-    cnt[i] = static_cast<uint32_t>(run);
-    run += c;
+  for (int base = 0; base < num_tiles; base += kRouteThreads * 8) {
+    const int i0 = base + tid * 8;
+    int c[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) c[j] = i0 + j < num_tiles ? static_cast<int>(__ldcg(cnt + i0 + j)) : 0;
+    int sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum += c[j];
+    int round_total = 0;
+    int run = total + block_exclusive_scan(sum, s_warp, &round_total);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (i0 + j < num_tiles) cnt[i0 + j] = static_cast<uint32_t>(run);
+      run += c[j];
+    }
+    total += round_total;
+    __syncthreads();     // s_warp is rewritten in the next round
   }
   if (tid == 0) {
     counts[0] = total;
@@ -359,7 +426,7 @@ static int route_launch(const uint8_t* mask, int M, int cap, int* perm, int* cou
     route_kernel<<<tiles, kRouteThreads, 0, stream>>>(mask, M, cap, perm, counts, ws, status);
     return cuda_status(cudaGetLastError());
   }
-  route_count_kernel<<<tiles, kRouteThreads, 0, stream>>>(mask, M, cap, counts, ws);
+  route_count_kernel<<<(tiles + kCountTiles - 1) / kCountTiles, kRouteThreads, 0, stream>>>(mask, M, cap, tiles, counts, ws);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_status(e);
   route_scatter_kernel<<<tiles, kRouteThreads, 0, stream>>>(mask, M, cap, perm, ws);
