@@ -409,6 +409,202 @@ __global__ void __launch_bounds__(kRouteThreads) route_scatter_kernel(const uint
   store_list_bulk(perm + cap + pre_t, s_t, tile_t, 128);
 }
 
+// -------------------------------------------------------------------------------------------
+// Long masks whose BITS fit in shared memory (one bit per token: 2^26 tokens are 8 MiB over the whole
+// GPU): one launch that reads the mask once.  The grid is exactly what the device holds at once (four
+// CTAs per SM); CTA c owns the consecutive tiles [c * T, (c + 1) * T).
+//   phase 1: read the owned mask bytes (four tiles' loads in flight per thread), keep them as bits in
+//            shared memory, count visual tokens and runs, publish the CTA's count;
+//   grid-wide wait (bounded: ST_TIMEOUT_GRID if the CTAs are not all resident at once);
+//   the CTA's exclusive prefix = sum of the counts published by the CTAs before it;
+//   phase 2: per tile scan + compaction from the bits, lists out by bulk copies as in the scatter kernel.
+// 5 bytes per token of DRAM traffic, no chain of prefixes, no second read of the mask.
+// ws: [0] run total, [1 .. 1 + gridDim) per-CTA visual count.
+// -------------------------------------------------------------------------------------------
+constexpr int kResidentPerSm = 4;
+constexpr int kResidentSlots = 64;
+constexpr int kResidentMaxCtas = 1024;
+// grid-wide wait counters, one slot per launch in turn; monotonic (launch n on a slot waits for
+// (n + 1) * gridDim arrivals, and the grid size never changes on a device), zero when the library is loaded
+static __device__ unsigned long long g_route_barrier[kResidentSlots];
+
+__device__ __forceinline__ unsigned long long route_ld_acquire_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// block-wide sums of two values; contains two __syncthreads()
+__device__ __forceinline__ void block_sum2(int a, int b, int (*s_red)[kRouteThreads / 32], int* out_a, int* out_b) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  a = __reduce_add_sync(0xFFFFFFFFu, a);
+  b = __reduce_add_sync(0xFFFFFFFFu, b);
+  __syncthreads();                       // earlier readers of s_red are done
+  if (lane == 0) { s_red[0][warp] = a; s_red[1][warp] = b; }
+  __syncthreads();
+  int ta = 0, tb = 0;
+#pragma unroll
+  for (int i = 0; i < kRouteThreads / 32; ++i) { ta += s_red[0][i]; tb += s_red[1][i]; }
+  *out_a = ta;
+  *out_b = tb;
+}
+
+__global__ void __launch_bounds__(kRouteThreads, kResidentPerSm)
+route_resident_kernel(const uint8_t* __restrict__ mask, int M, int cap, int num_tiles, int tiles_per_cta,
+                      int* __restrict__ perm, int* __restrict__ counts, uint32_t* __restrict__ ws, int slot,
+                      int* __restrict__ status) {
+  extern __shared__ __align__(16) int s_dyn[];   // list staging of one tile, then the owned tiles' bits (256 words a tile)
+  int* s_list = s_dyn;
+  uint32_t* s_bits = reinterpret_cast<uint32_t*>(s_dyn + kRouteTile + 16);
+  __shared__ int s_warp[kRouteThreads / 32];
+  __shared__ int s_red[2][kRouteThreads / 32];
+  __shared__ int s_ok;
+  const int tid = threadIdx.x;
+  const int tile_begin = blockIdx.x * tiles_per_cta;
+  const int my_tiles = max(0, min(tiles_per_cta, num_tiles - tile_begin));
+  const bool aligned = (reinterpret_cast<uintptr_t>(mask) & 15) == 0;
+
+  // ---- phase 1: mask bytes -> bits in shared memory
+  int nv = 0;
+  for (int t0 = 0; t0 < my_tiles; t0 += kCountTiles) {
+    uint32_t bits[kCountTiles];
+    if (aligned && static_cast<int64_t>(tile_begin + t0 + kCountTiles) * kRouteTile <= M) {
+      uint4 v[kCountTiles][2];
+#pragma unroll
+      for (int j = 0; j < kCountTiles; ++j) {
+        const int base = (tile_begin + t0 + j) * kRouteTile + tid * kRoutePerThread;
+        v[j][0] = *reinterpret_cast<const uint4*>(mask + base);
+        v[j][1] = *reinterpret_cast<const uint4*>(mask + base + 16);
+      }
+#pragma unroll
+      for (int j = 0; j < kCountTiles; ++j) {
+        const uint32_t w[8] = {v[j][0].x, v[j][0].y, v[j][0].z, v[j][0].w, v[j][1].x, v[j][1].y, v[j][1].z, v[j][1].w};
+        bits[j] = mask_words_to_bits(w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kCountTiles; ++j)
+        bits[j] = load_thread_tokens(mask, M, (tile_begin + t0 + j) * kRouteTile + tid * kRoutePerThread).bits;
+    }
+#pragma unroll
+    for (int j = 0; j < kCountTiles; ++j) {
+      if (t0 + j < my_tiles) {
+        s_bits[(t0 + j) * kRouteThreads + tid] = bits[j];
+        nv += __popc(bits[j]);
+      }
+    }
+  }
+  __syncthreads();
+  // runs: a token whose modality differs from its predecessor's (token 0 always); the predecessor of a
+  // word's first token is the last bit of the word before it in shared memory
+  int nruns = 0;
+  for (int t = 0; t < my_tiles; ++t) {
+    const int base = (tile_begin + t) * kRouteTile + tid * kRoutePerThread;
+    const int valid = min(kRoutePerThread, M - base);
+    if (valid > 0) {
+      const uint32_t b = s_bits[t * kRouteThreads + tid];
+      uint32_t prev;
+      if (t == 0 && tid == 0) prev = base > 0 ? (mask[base - 1] != 0 ? 1u : 0u) : ((b & 1u) ^ 1u);
+      else prev = s_bits[t * kRouteThreads + tid - 1] >> 31;
+      const uint32_t vmask = valid == 32 ? 0xFFFFFFFFu : ((1u << valid) - 1u);
+      nruns += __popc((b ^ ((b << 1) | prev)) & vmask);
+    }
+  }
+  int cta_v = 0, cta_runs = 0;
+  block_sum2(nv, nruns, s_red, &cta_v, &cta_runs);
+
+  // ---- publish, then wait for the whole grid
+  if (tid == 0) {
+    ws[1 + blockIdx.x] = static_cast<uint32_t>(cta_v);
+    if (cta_runs) atomicAdd(&ws[0], static_cast<uint32_t>(cta_runs));
+    __threadfence();
+    unsigned long long* bar = &g_route_barrier[slot];
+    const unsigned long long ticket = atomicAdd(bar, 1ULL);
+    const unsigned long long target = (ticket / gridDim.x + 1ULL) * gridDim.x;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t polls = 0;
+    int ok = 1;
+    while (route_ld_acquire_u64(bar) < target) {
+      if ((++polls & 63u) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+        atomicCAS(status, 0, ST_TIMEOUT_GRID);
+        ok = 0;
+        break;
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+
+  // ---- visual tokens before this CTA's first tile, and in all
+  int part = 0, all = 0;
+  for (int j = tid; j < static_cast<int>(gridDim.x); j += kRouteThreads) {
+    const int c = static_cast<int>(__ldcg(ws + 1 + j));
+    all += c;
+    if (j < static_cast<int>(blockIdx.x)) part += c;
+  }
+  int pre_v = 0, total_v = 0;
+  block_sum2(part, all, s_red, &pre_v, &total_v);
+  if (blockIdx.x == 0 && tid == 0) {
+    counts[0] = total_v;
+    counts[1] = M - total_v;
+    counts[2] = cap;
+    counts[3] = M;
+    counts[4] = static_cast<int>(__ldcg(ws));
+  }
+
+  // ---- phase 2: lists
+  for (int t = 0; t < my_tiles; ++t) {
+    const int tile = tile_begin + t;
+    const uint32_t b = s_bits[t * kRouteThreads + tid];
+    int tile_v = 0;
+    const int ev = block_exclusive_scan(__popc(b), s_warp, &tile_v);
+    const int tile_len = min(kRouteTile, M - tile * kRouteTile);
+    const int valid = max(0, min(kRoutePerThread, tile_len - tid * kRoutePerThread));
+    const int tile_t = tile_len - tile_v;
+    const int pre_t = tile * kRouteTile - pre_v;
+    int* s_v = s_list + (pre_v & 3);
+    int* s_t = s_list + ((((pre_v & 3) + tile_v + 3) & ~3) + ((cap + pre_t) & 3));
+    compact_tile(s_v, s_t, tile, b, ev, valid);
+    __syncthreads();
+    store_list_bulk(perm + pre_v, s_v, tile_v, 0);
+    store_list_bulk(perm + cap + pre_t, s_t, tile_t, 128);
+    pre_v += tile_v;
+    __syncthreads();      // the bulk copies have read the lists: the next tile may overwrite them
+  }
+}
+
+// Largest number of tiles per CTA for which kResidentPerSm CTAs of the resident kernel fit on an SM
+// (0: the kernel cannot be used on this device); found once per process.
+static int resident_max_tiles_per_cta() {
+  static int cached = -1;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached >= 0) return cached;
+  cached = 0;
+  const DeviceInfo& dev = device_info();
+  if (dev.sm_count * kResidentPerSm > kResidentMaxCtas) return cached;
+  for (int t = 40; t >= 1; --t) {
+    const size_t smem = (kRouteTile + 16) * sizeof(int) + static_cast<size_t>(t) * kRouteThreads * sizeof(uint32_t);
+    if (smem > static_cast<size_t>(dev.smem_optin)) continue;
+    if (cudaFuncSetAttribute(route_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      continue;
+    }
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, route_resident_kernel, kRouteThreads, smem) != cudaSuccess) {
+      cudaGetLastError();
+      continue;
+    }
+    if (blocks >= kResidentPerSm) {
+      cached = t;
+      break;
+    }
+  }
+  return cached;
+}
+
 __global__ void route_empty_kernel(int* counts, int cap) {
   counts[0] = 0; counts[1] = 0; counts[2] = cap; counts[3] = 0; counts[4] = 0;
 }
@@ -418,6 +614,19 @@ __global__ void route_empty_kernel(int* counts, int cap) {
 static int route_launch(const uint8_t* mask, int M, int cap, int* perm, int* counts, uint32_t* ws, int* status,
                         cudaStream_t stream) {
   const int tiles = (M + kRouteTile - 1) / kRouteTile;
+  if (tiles > kLookBackMaxTiles) {
+    const int grid = device_info().sm_count * kResidentPerSm;
+    const int per_cta = (tiles + grid - 1) / grid;
+    if (per_cta <= resident_max_tiles_per_cta()) {
+      cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(uint32_t), stream);      // the run total
+      if (e != cudaSuccess) return cuda_status(e);
+      static unsigned launch_seq = 0;   // successive launches take successive barrier slots
+      const int slot = static_cast<int>(__atomic_fetch_add(&launch_seq, 1u, __ATOMIC_RELAXED) % kResidentSlots);
+      const size_t smem = (kRouteTile + 16) * sizeof(int) + static_cast<size_t>(per_cta) * kRouteThreads * sizeof(uint32_t);
+      route_resident_kernel<<<grid, kRouteThreads, smem, stream>>>(mask, M, cap, tiles, per_cta, perm, counts, ws, slot, status);
+      return cuda_status(cudaGetLastError());
+    }
+  }
   if (tiles > 1) {
     cudaError_t e = cudaMemsetAsync(ws, 0, (static_cast<size_t>(tiles) + 2) * sizeof(uint32_t), stream);
     if (e != cudaSuccess) return cuda_status(e);
@@ -440,8 +649,9 @@ using namespace ffnk;
 extern "C" int64_t ffnk_route_capacity(int64_t M) { return ((M + 127) / 128) * 128; }
 
 extern "C" int64_t ffnk_route_workspace_bytes(int64_t M) {
+  // one word per tile (count + scatter) or per CTA of the resident kernel, plus the run total and a counter
   const int64_t tiles = (M + kRouteTile - 1) / kRouteTile;
-  return (tiles + 2) * static_cast<int64_t>(sizeof(uint32_t));
+  return ((tiles > kResidentMaxCtas ? tiles : kResidentMaxCtas) + 2) * static_cast<int64_t>(sizeof(uint32_t));
 }
 
 extern "C" int ffnk_route(const void* mask, int64_t M, int32_t* perm, int32_t* counts, void* workspace,

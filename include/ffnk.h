@@ -61,6 +61,12 @@ int ffnk_version(void);
  *   counts int32[8] = { Mv, Mt, cap, M, runs, -, -, - }   (stay on the device; no host sync)
  *          runs = number of maximal stretches of consecutive same-modality tokens
  *   workspace: ffnk_route_workspace_bytes(M) bytes, cleared by the call itself
+ * Masks of more than 2^20 tokens whose bits fit in the GPU's shared memory (one bit per token; 2^26
+ * tokens are 8 MiB) are routed by ONE kernel whose CTAs wait for one another once: the barrier-counter
+ * rule of ffnk_ffn_decode applies to it (its counters are this library's own, one per launch in turn
+ * over 64 slots; a grid that is not resident all at once reports the status "grid-wide wait expired"
+ * instead of hanging), and its first call on a process queries the occupancy of that kernel: make it
+ * outside any stream capture.
  * ------------------------------------------------------------------------------------- */
 int64_t ffnk_route_capacity(int64_t M);
 int64_t ffnk_route_workspace_bytes(int64_t M);
