@@ -43,6 +43,7 @@ struct TuneOverrides {
   int max_run_rows = -1;    // largest tiled TMA box for runs of consecutive tokens (0: gather4 only)
   int copy_threshold = -1;  // average run length below which MaskedLinear forward copies a to routed order
   int verbose = -1;         // 1: print the arguments of a tensor map the driver rejects
+  int route_resident = -1;  // 0: long masks never take the one-launch resident routing kernel (count + scatter instead)
 };
 TuneOverrides& tune_overrides();
 

@@ -617,7 +617,7 @@ static int route_launch(const uint8_t* mask, int M, int cap, int* perm, int* cou
   if (tiles > kLookBackMaxTiles) {
     const int grid = device_info().sm_count * kResidentPerSm;
     const int per_cta = (tiles + grid - 1) / grid;
-    if (per_cta <= resident_max_tiles_per_cta()) {
+    if (tune_overrides().route_resident != 0 && per_cta <= resident_max_tiles_per_cta()) {
       cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(uint32_t), stream);      // the run total
       if (e != cudaSuccess) return cuda_status(e);
       static unsigned launch_seq = 0;   // successive launches take successive barrier slots

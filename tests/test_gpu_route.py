@@ -24,10 +24,23 @@ def _check(mask_cpu, dev):
 
 
 @pytest.mark.parametrize("M", [1, 2, 15, 16, 17, 127, 128, 129, 1000, 4095, 4096, 4097, 4099, 8192, 65537, 1 << 20,
-                               (1 << 20) + 1, 3000001])   # the last two: more than 128 tiles, the two-kernel path
+                               (1 << 20) + 1, 3000001])   # the last two: more than 128 tiles, the one-launch resident kernel
 @pytest.mark.parametrize("kind", ["bernoulli", "all_visual", "all_text", "alternating", "span"])
 def test_route_bit_exact(dev, M, kind):
     _check(edge_mask(M, kind, seed=M), dev)
+
+
+@pytest.mark.parametrize("M", [(1 << 20) + 1, 3000001, (1 << 22) + 8192 * 3 + 5])
+@pytest.mark.parametrize("kind", ["bernoulli", "all_visual", "alternating", "span"])
+def test_route_count_and_scatter_kernels(dev, M, kind):
+    # the path of masks too long for the resident kernel (count, then scatter), forced at sizes a test can afford
+    from ffn_kernel_b200._lib import lib
+    L = lib()
+    assert L.ffnk_tune_override(b"route_resident", 0) == 0
+    try:
+        _check(edge_mask(M, kind, seed=M), dev)
+    finally:
+        assert L.ffnk_tune_override(b"route_resident", -1) == 0
 
 
 def test_route_uint8_mask_nonzero_is_visual(dev):
