@@ -30,6 +30,9 @@ SIGNATURES = {
     "ffnk_linear_bwd_parts": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
                                       c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "ffnk_route_permute_max_tokens": (c_int64, []),
+    "ffnk_route_permute_rows": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                        c_int64, c_void_p]),
     "ffnk_permute_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                   c_void_p]),
     "ffnk_ffn_gateup": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

@@ -75,16 +75,23 @@ extern "C" int ffnk_ffn_forward(const void* x, int64_t ldx, const void* w1, cons
 
   int32_t* perm = reinterpret_cast<int32_t*>(ws + w.perm);
   int32_t* counts = reinterpret_cast<int32_t*>(ws + w.counts);
-  int r = ffnk_route(mask, M, perm, counts, ws + w.scan, status, stream);
-  if (r) return r;
+  int r;
   const void* a = x;
   int64_t lda = ldx;
   int routed_in = 0;
   if (permute_first(M, d, h)) {
-    if ((r = ffnk_permute_rows(x, ldx, perm, counts, ws + w.xr, d, M, d, stream))) return r;
+    // a mask of a single routing tile is routed by the kernel that copies the rows: one launch fewer
+    if (M <= ffnk_route_permute_max_tokens()) {
+      if ((r = ffnk_route_permute_rows(mask, M, x, ldx, d, perm, counts, ws + w.xr, d, stream))) return r;
+    } else {
+      if ((r = ffnk_route(mask, M, perm, counts, ws + w.scan, status, stream))) return r;
+      if ((r = ffnk_permute_rows(x, ldx, perm, counts, ws + w.xr, d, M, d, stream))) return r;
+    }
     a = ws + w.xr;
     lda = d;
     routed_in = 1;
+  } else if ((r = ffnk_route(mask, M, perm, counts, ws + w.scan, status, stream))) {
+    return r;
   }
   if ((r = ffnk_ffn_gateup(a, lda, w1, w3, u1, u3, w13_stride_k, w13_stride_n, perm, counts, ws + w.inter, h,
                            routed_in, 1, M, d, h, status, stream)))

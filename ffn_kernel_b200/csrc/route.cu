@@ -717,11 +717,96 @@ __global__ void __launch_bounds__(kPermuteThreads) permute_rows_kernel(const uin
     }
   }
 }
+
+// Routing and the copy into routed order in ONE launch, for masks of a single tile (M <= 8192): every CTA
+// routes the whole mask for itself (8 KiB of mask out of L2, a block scan and a compaction in shared
+// memory: a few microseconds, less than a second launch costs), CTA 0 also writes perm and counts for the
+// GEMMs that follow, and then every warp copies its share of the rows, reading the row list from shared
+// memory.  Same results as route_kernel followed by permute_rows_kernel.
+__global__ void __launch_bounds__(kRouteThreads) route_permute_kernel(const uint8_t* __restrict__ mask, int M, int cap,
+                                                                      int* __restrict__ perm, int* __restrict__ counts,
+                                                                      const uint4* __restrict__ x, int64_t ldx16,
+                                                                      uint4* __restrict__ out, int64_t ldo16, int chunks) {
+  __shared__ int s_list[kRouteTile];   // visual tokens ascending, then text tokens ascending
+  __shared__ int s_warp[kRouteThreads / 32];
+  __shared__ int s_runs;
+  const int tid = threadIdx.x;
+  const ThreadTokens tt = load_thread_tokens(mask, M, tid * kRoutePerThread);
+  if (tid == 0) s_runs = 0;
+  int Mv = 0;
+  const int ev = block_exclusive_scan(__popc(tt.bits), s_warp, &Mv);
+  if (blockIdx.x == 0) {
+    const int wr = __reduce_add_sync(0xFFFFFFFFu, tt.nruns);
+    if ((tid & 31) == 0 && wr) atomicAdd(&s_runs, wr);
+  }
+  compact_tile(s_list, s_list + Mv, 0, tt.bits, ev, tt.valid);
+  __syncthreads();
+  const int Mt = M - Mv;
+  if (blockIdx.x == 0) {
+    for (int i = tid; i < Mv; i += kRouteThreads) perm[i] = s_list[i];
+    for (int i = tid; i < Mt; i += kRouteThreads) perm[cap + i] = s_list[Mv + i];
+    if (tid == 0) {
+      counts[0] = Mv;
+      counts[1] = Mt;
+      counts[2] = cap;
+      counts[3] = M;
+      counts[4] = s_runs;
+    }
+  }
+  const int text_base = ((Mv + 255) >> 8) << 8;
+  const int warps_per_block = kRouteThreads / 32;
+  const int lane = tid & 31;
+  for (int i = blockIdx.x * warps_per_block + (tid >> 5); i < M; i += gridDim.x * warps_per_block) {
+    const int tok = s_list[i];
+    const int64_t dst = i >= Mv ? static_cast<int64_t>(text_base) + (i - Mv) : i;
+    const uint4* src_row = x + static_cast<int64_t>(tok) * ldx16;
+    uint4* dst_row = out + dst * ldo16;
+    for (int c = lane; c < chunks; c += 128) {
+      uint4 v0, v1, v2, v3;
+      const bool b1 = c + 32 < chunks, b2 = c + 64 < chunks, b3 = c + 96 < chunks;
+      v0 = __ldg(src_row + c);
+      if (b1) v1 = __ldg(src_row + c + 32);
+      if (b2) v2 = __ldg(src_row + c + 64);
+      if (b3) v3 = __ldg(src_row + c + 96);
+      dst_row[c] = v0;
+      if (b1) dst_row[c + 32] = v1;
+      if (b2) dst_row[c + 64] = v2;
+      if (b3) dst_row[c + 96] = v3;
+    }
+  }
+}
 }  // namespace ffnk
 
 namespace ffnk {
 int permute_rows_launch(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out, int64_t ldo,
                         int64_t M, int64_t d, int only_if_scattered, void* stream_);
+}
+
+extern "C" int64_t ffnk_route_permute_max_tokens(void) { return kRouteTile; }
+
+extern "C" int ffnk_route_permute_rows(const void* mask, int64_t M, const void* x, int64_t ldx, int64_t d, int32_t* perm,
+                                       int32_t* counts, void* out, int64_t ldo, void* stream_) {
+  if (!counts) return FFNK_ERR_NULL;
+  if (M < 0 || M > kRouteTile) return FFNK_ERR_SHAPE;
+  const int cap = static_cast<int>(ffnk_route_capacity(M));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M == 0) {
+    route_empty_kernel<<<1, 1, 0, stream>>>(counts, cap);
+    return cuda_status(cudaGetLastError());
+  }
+  if (!mask || !x || !perm || !out) return FFNK_ERR_NULL;
+  if (d < 8 || (d & 7) || d >= (1ll << 30)) return FFNK_ERR_SHAPE;
+  if ((ldx & 7) || (ldo & 7) || ldx < d || ldo < d || (reinterpret_cast<uintptr_t>(x) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(perm) & 15))
+    return FFNK_ERR_ALIGN;
+  const DeviceInfo& dev = device_info();
+  int64_t blocks = (M + 7) / 8;
+  const int64_t max_blocks = static_cast<int64_t>(dev.sm_count) * 4;
+  if (blocks > max_blocks) blocks = max_blocks;
+  route_permute_kernel<<<static_cast<unsigned>(blocks), kRouteThreads, 0, stream>>>(
+      static_cast<const uint8_t*>(mask), static_cast<int>(M), cap, perm, counts, static_cast<const uint4*>(x), ldx / 8,
+      static_cast<uint4*>(out), ldo / 8, static_cast<int>(d / 8));
+  return cuda_status(cudaGetLastError());
 }
 
 extern "C" int ffnk_permute_rows(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out,

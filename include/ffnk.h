@@ -150,6 +150,15 @@ int ffnk_linear_bwd_parts(const void* g, int64_t ldg, const void* a, int64_t lda
 int ffnk_permute_rows(const void* x, int64_t ldx, const int32_t* perm, const int32_t* counts, void* out, int64_t ldo,
                       int64_t M, int64_t d, void* stream);
 
+/* ffnk_route followed by ffnk_permute_rows in ONE launch, for masks of at most
+ * ffnk_route_permute_max_tokens() (8192) tokens: every CTA routes the whole mask for itself in shared memory
+ * and copies its share of the rows; perm and counts come out as from ffnk_route.  Needs no workspace and
+ * reports no device status (nothing in it waits).  The MaskedFFN forward uses it below that size whenever
+ * it copies x first. */
+int64_t ffnk_route_permute_max_tokens(void);
+int ffnk_route_permute_rows(const void* mask, int64_t M, const void* x, int64_t ldx, int64_t d, int32_t* perm,
+                            int32_t* counts, void* out, int64_t ldo, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * MaskedFFN gate/up projection with the SwiGLU epilogue.  Replaces _bf16_ffn_forward
  * (ffn_kernel/ffn.py:527-560) and _masked_ffn_infer (ffn_kernel/ffn.py:15-113):

@@ -84,3 +84,47 @@ def test_route_rejects_bad_arguments(dev):
         route(torch.zeros(4, 4, dtype=torch.bool, device=dev))
     with pytest.raises(RuntimeError):
         route(torch.zeros(4, dtype=torch.float32, device=dev))
+
+
+@pytest.mark.parametrize("M", [1, 7, 127, 129, 1000, 4099, 8191, 8192])
+@pytest.mark.parametrize("kind", ["bernoulli", "all_visual", "all_text", "alternating", "span"])
+def test_route_and_row_copy_in_one_launch(dev, M, kind):
+    # ffnk_route_permute_rows against ffnk_route followed by ffnk_permute_rows: same lists, counts and rows
+    from ffn_kernel_b200 import check_status
+    from ffn_kernel_b200._lib import lib
+    from ffn_kernel_b200.route import stream_ptr
+    L = lib()
+    d = 264
+    mask = edge_mask(M, kind, seed=M).to(dev)
+    x = torch.randn((M, d), generator=torch.Generator().manual_seed(M)).to(torch.bfloat16).to(dev)
+    rt = route(mask)
+    rows = rt.cap + 512
+    ref = torch.full((rows, d), 7.0, device=dev, dtype=torch.bfloat16)
+    got = ref.clone()
+    assert L.ffnk_permute_rows(x.data_ptr(), d, rt.perm.data_ptr(), rt.counts.data_ptr(), ref.data_ptr(), d, M, d,
+                               stream_ptr(dev)) == 0
+    perm = torch.full_like(rt.perm, -1)
+    counts = torch.full_like(rt.counts, -1)
+    assert L.ffnk_route_permute_rows(mask.data_ptr(), M, x.data_ptr(), d, d, perm.data_ptr(), counts.data_ptr(),
+                                     got.data_ptr(), d, stream_ptr(dev)) == 0
+    torch.cuda.synchronize()
+    check_status()
+    assert counts.tolist()[:5] == rt.counts.tolist()[:5]
+    mv, mt = counts.tolist()[:2]
+    assert torch.equal(perm[:mv], rt.perm[:mv]) and torch.equal(perm[rt.cap:rt.cap + mt], rt.perm[rt.cap:rt.cap + mt])
+    assert torch.equal(got, ref)          # the rows between and after the groups keep their fill
+
+
+def test_route_and_row_copy_arguments(dev):
+    from ffn_kernel_b200._lib import lib
+    from ffn_kernel_b200.route import stream_ptr
+    L = lib()
+    assert L.ffnk_route_permute_max_tokens() == 8192
+    buf = torch.zeros(4096, device=dev, dtype=torch.int32)
+    p = buf.data_ptr()
+    assert L.ffnk_route_permute_rows(p, 8193, p, 8, 8, p, p, p, 8, stream_ptr(dev)) < 0      # more than one tile
+    assert L.ffnk_route_permute_rows(p, 16, p, 8, 12, p, p, p, 16, stream_ptr(dev)) < 0      # d not a multiple of 8
+    assert L.ffnk_route_permute_rows(None, 16, p, 8, 8, p, p, p, 8, stream_ptr(dev)) < 0
+    assert L.ffnk_route_permute_rows(p, 0, None, 8, 8, None, p, None, 8, stream_ptr(dev)) == 0   # empty mask: counts only
+    torch.cuda.synchronize()
+    assert buf[:5].tolist() == [0, 0, 0, 0, 0]
