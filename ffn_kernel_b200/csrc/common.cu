@@ -129,7 +129,8 @@ extern "C" int ffnk_tune_override(const char* name, int value) {
   struct { const char* n; int* v; } table[] = {
       {"pair", &t.pair}, {"narrow", &t.narrow}, {"permute", &t.permute}, {"epi_warps", &t.epi_warps},
       {"group_m", &t.group_m}, {"wgrad_pair", &t.wgrad_pair}, {"max_run_rows", &t.max_run_rows},
-      {"copy_threshold", &t.copy_threshold}, {"verbose", &t.verbose}, {"route_resident", &t.route_resident}};
+      {"copy_threshold", &t.copy_threshold}, {"verbose", &t.verbose}, {"route_resident", &t.route_resident},
+      {"ksplit", &t.ksplit}};
   for (auto& e : table)
     if (strcmp(e.n, name) == 0) {
       *e.v = value;

@@ -23,7 +23,7 @@ static bool permute_first(int64_t M, int64_t d, int64_t h) {
 }
 
 struct FfnWorkspace {
-  int64_t perm, counts, scan, xr, inter, total;
+  int64_t perm, counts, scan, xr, inter, kpart, kpart_bytes, total;
 };
 
 static FfnWorkspace ffn_workspace(int64_t M, int64_t d, int64_t h) {
@@ -40,6 +40,9 @@ static FfnWorkspace ffn_workspace(int64_t M, int64_t d, int64_t h) {
   if (permute_first(M, d, h)) off += align256((cap + 512) * d * 2);
   w.inter = off;
   off += align256((cap + 512) * h * 2);
+  w.kpart = off;
+  w.kpart_bytes = ffn_down_scratch_bytes(M, d, h);     // partial tiles of a split-K down projection (few row tiles)
+  off += align256(w.kpart_bytes);
   w.total = off;
   return w;
 }
@@ -96,6 +99,6 @@ extern "C" int ffnk_ffn_forward(const void* x, int64_t ldx, const void* w1, cons
   if ((r = ffnk_ffn_gateup(a, lda, w1, w3, u1, u3, w13_stride_k, w13_stride_n, perm, counts, ws + w.inter, h,
                            routed_in, 1, M, d, h, status, stream)))
     return r;
-  return ffnk_ffn_down(ws + w.inter, h, w2, u2, w2_stride_k, w2_stride_n, perm, counts, y, ldy, M, d, h, status,
-                       stream);
+  return ffn_down_with_scratch(ws + w.inter, h, w2, u2, w2_stride_k, w2_stride_n, perm, counts, y, ldy, M, d, h,
+                               w.kpart_bytes ? ws + w.kpart : nullptr, w.kpart_bytes, status, stream);
 }

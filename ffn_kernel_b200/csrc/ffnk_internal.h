@@ -44,11 +44,19 @@ struct TuneOverrides {
   int copy_threshold = -1;  // average run length below which MaskedLinear forward copies a to routed order
   int verbose = -1;         // 1: print the arguments of a tensor map the driver rejects
   int route_resident = -1;  // 0: long masks never take the one-launch resident routing kernel (count + scatter instead)
+  int ksplit = -1;          // down projection of the FFN forward: 0/1 never split K, n > 1 split n ways wherever it can
 };
 TuneOverrides& tune_overrides();
 
 // Diagnostics buffer installed by ffnk_debug_profile_buffer (null when off): 8 int64 per CTA.
 long long* debug_profile_buffer();
+
+// ffnk_ffn_down with an optional scratch buffer (16-byte aligned) for the fp32 partial tiles of its split-K
+// variant, which it takes for few row tiles when ffn_down_scratch_bytes(M, d, h) > 0 bytes are given.
+int64_t ffn_down_scratch_bytes(int64_t M, int64_t d, int64_t h);
+int ffn_down_with_scratch(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
+                          int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy, int64_t M,
+                          int64_t d, int64_t h, void* scratch, int64_t scratch_bytes, int32_t* status, void* stream);
 
 // permute_rows with an optional device-side gate: with only_if_scattered = T > 0 the kernel returns at
 // once unless the mask's runs of same-modality tokens average fewer than T rows.

@@ -26,6 +26,8 @@
 // under the main loop of tile i+1.
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "ffnk_internal.h"
 #include "ptx.cuh"
 
@@ -102,7 +104,21 @@ struct GemmParams {
   int peer_world = 0;
   int peer_rank = 0;
   int peer_rows = 1;
+  // Split-K (A_ROUTED + EPI_STORE + OUT_SCATTER, single CTAs, K-major weights): ksplit > 1 makes every tile
+  // ksplit work items, one per range of k-steps; the items leave fp32 partial tiles in kpart
+  // [item][BN_T / 4 column groups][128 rows][4] and the one that arrives last at the tile's counter adds them in item
+  // order and stores the rows.  kcount: one counter per tile, zero before and after the launch.
+  int ksplit = 1;
+  float* kpart = nullptr;
+  unsigned int* kcount = nullptr;
 };
+
+// Split-K arrival counters, one row of kSplitKTiles per launch in turn (launches that could overlap on the
+// device get different rows); the last arrival at a tile resets its counter, so the rows stay zero between
+// launches.  Zero when the library is loaded.
+constexpr int kSplitKSlots = 64;
+constexpr int kSplitKTiles = 256;
+static __device__ unsigned int g_splitk_count[kSplitKSlots][kSplitKTiles];
 
 // Views of one row-gathered activation matrix: m[0] fetches single rows (gather4); m[1 + i]
 // fetches boxes of 4 << i consecutive rows (4, 8, ..., 128), 64 columns wide.
@@ -419,6 +435,66 @@ __device__ __forceinline__ void epilogue_rows_staged(uint32_t taddr, const GemmP
   }
 }
 
+// The same row store with the values taken from `nsplit` (at most kMaxSplitK) fp32 partial tiles in memory
+// (split-K), added in item order.  A partial tile is stored as [BN_T / 4 column groups][128 rows] of float4,
+// so that the 32 lanes of a warp (32 rows) touch 512 contiguous bytes per access; `src` is this lane's row
+// in column group 0 of the first partial tile, `stride` the float4 between tiles.  Sixteen columns of every
+// partial tile are requested before any is added (up to sixteen 16-byte loads in flight per thread: a
+// load-add loop would pay the L2 latency once per split and group).
+constexpr int kMaxSplitK = 4;
+template <int BN_T>
+__device__ __forceinline__ void epilogue_rows_from_partials(const float4* src, int nsplit, int64_t stride, const GemmParams& p,
+                                                           __nv_bfloat16* dst, int n_base, int part, int parts,
+                                                           uint8_t* stg, int lane) {
+  constexpr int CH = BN_T / 64;
+  const unsigned long long dptr = reinterpret_cast<unsigned long long>(dst);
+  const int piece = lane & 7;
+#pragma unroll 1
+  for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
+#pragma unroll 1
+    for (int jp = 0; jp < 4; ++jp) {
+      float4 t[kMaxSplitK][4];
+#pragma unroll
+      for (int sp = 0; sp < kMaxSplitK; ++sp) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) t[sp][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src != nullptr && sp < nsplit) {
+          const float4* q = src + sp * stride + (c * 16 + jp * 4) * BM;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) t[sp][k] = __ldcg(q + k * BM);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+#pragma unroll
+        for (int sp = 1; sp < kMaxSplitK; ++sp) {
+          t[0][k].x += t[sp][k].x;
+          t[0][k].y += t[sp][k].y;
+          t[0][k].z += t[sp][k].z;
+          t[0][k].w += t[sp][k].w;
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int j = jp * 2 + jj;
+        const float a[8] = {t[0][2 * jj].x,     t[0][2 * jj].y,     t[0][2 * jj].z,     t[0][2 * jj].w,
+                            t[0][2 * jj + 1].x, t[0][2 * jj + 1].y, t[0][2 * jj + 1].z, t[0][2 * jj + 1].w};
+        *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = pack_bf16x8(a);
+      }
+    }
+    __syncwarp();
+    const int n0 = n_base + c * 64 + piece * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 4 + (lane >> 3);
+      const unsigned long long rp = __shfl_sync(0xFFFFFFFFu, dptr, r);
+      const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128 + ((piece ^ (r & 7)) << 4));
+      if (rp != 0ull && n0 < p.n_out) *reinterpret_cast<uint4*>(rp + static_cast<unsigned long long>(n0) * 2ull) = val;
+    }
+    __syncwarp();
+  }
+}
+
 // BN_T = 128 (6 stages of 32 KiB) sits between the two.
 // BN_T = 256 is the throughput tile; BN_T = 64 (K-major weights only) spreads a problem with few row
 // tiles over more SMs: 8 stages of 24 KiB, four times as many column tiles.
@@ -478,6 +554,10 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
   const int total_tiles = m_tiles * n_tiles;
   const int k_steps0 = (p.k_len + BK - 1) / BK;                 // first contraction segment
   const int k_steps = k_steps0 + (p.k_len1 + BK - 1) / BK;      // plus the optional second one
+  // split-K: work item = (tile, range of k-steps); consecutive CTAs take the ranges of one tile
+  constexpr bool SPLITK = A_MODE == A_ROUTED && EPI == EPI_STORE && OUT_MODE == OUT_SCATTER && !B_MN;
+  const int nsplit = SPLITK ? p.ksplit : 1;
+  const int total_items = total_tiles * nsplit;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -486,7 +566,9 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
     int issued = 0;
     bool ok = true;
     const bool via_copy = (A_MODE == A_GATHER) && p.a_copy && mask_is_scattered(p.counts, p.a_copy);
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int t = item / nsplit, split = item - t * nsplit;
+      const int ks_begin = split * k_steps / nsplit, ks_end = (split + 1) * k_steps / nsplit;
       const TileCoord tc = decode_tile(t, tiles_v, m_tiles, n_tiles, p.group_m, Mv, Mt, cap);
       int r0 = p.pad_row, r1 = p.pad_row, r2 = p.pad_row, r3 = p.pad_row;
       // How this lane's rows are fetched: as part of a tiled box of 4 * run_lanes consecutive
@@ -508,7 +590,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       const CUtensorMap* run_map = &am.m[run_lanes > 0 ? 32 - __clz(run_lanes) : 0];
       const CUtensorMap* mB0 = tc.text ? &tmBt0 : &tmBv0;
       const CUtensorMap* mB1 = tc.text ? &tmBt1 : &tmBv1;
-      for (int ks = 0; ks < k_steps; ++ks) {
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
         int w = 1;
         if (lane == 0) w = mbar_wait(&empty[stage], phase ^ 1, abort_flag) ? 1 : 0;
         w = __shfl_sync(0xFFFFFFFFu, w, 0);
@@ -582,7 +664,9 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       int it = 0;
       bool ok = true;
       long long t_begin = clock64(), t_full = 0, t_tmem = 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
+        const int split = item % nsplit;
+        const int ks_begin = split * k_steps / nsplit, ks_end = (split + 1) * k_steps / nsplit;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         long long tw = clock64();
@@ -593,7 +677,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
         t_tmem += clock64() - tw;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN_T;
-        for (int ks = 0; ks < k_steps; ++ks) {
+        for (int ks = ks_begin; ks < ks_end; ++ks) {
           tw = clock64();
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             report(p.status, ST_TIMEOUT_MMA_FULL);
@@ -609,7 +693,7 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
             const uint64_t da = umma_smem_desc(a_addr + kk * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(b_addr + kk * (UMMA_K * 128), TB_BYTES / 4, 1024)
                                      : umma_smem_desc(b_addr + kk * (UMMA_K * 2), 16, 1024);
-            umma_bf16<1>(tmem_d, da, db, idesc, (ks | kk) != 0 ? 1u : 0u);
+            umma_bf16<1>(tmem_d, da, db, idesc, (ks > ks_begin || kk != 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
           if (++stage == TSTAGES) { stage = 0; phase ^= 1; }
@@ -630,7 +714,8 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
     const int part = (warp - 2) >> 2;    // which half of the columns it drains
     const int row = q * 32 + lane;       // row of the tile held by this thread
     int it = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
+      const int t = item / nsplit;
       const TileCoord tc = decode_tile(t, tiles_v, m_tiles, n_tiles, p.group_m, Mv, Mt, cap);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -651,6 +736,48 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN_T;
+      if constexpr (SPLITK) {
+        if (nsplit > 1) {
+          // this item's partial tile out (rows that exist only), the accumulator back to the MMA warp at once
+          const int parts = epilogue_parts();
+          float4* mine = reinterpret_cast<float4*>(p.kpart) + static_cast<int64_t>(item) * (BN_T / 4) * BM + row;
+          constexpr int CH32 = BN_T / 32;
+#pragma unroll 1
+          for (int c = part * CH32 / parts; c < (part + 1) * CH32 / parts; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c * 32, v);
+            tmem_ld_wait();
+            if (valid) {
+#pragma unroll
+              for (int e = 0; e < 32; e += 4)
+                __stcg(mine + (c * 8 + e / 4) * BM,
+                       make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                                   __uint_as_float(v[e + 3])));
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
+          __threadfence();
+          int* s_last = reinterpret_cast<int*>(const_cast<int*>(abort_flag) + 1);
+          asm volatile("bar.sync 1, %0;" ::"r"(128 * parts) : "memory");
+          if (warp == 2 && lane == 0) {
+            const unsigned int old = atomicAdd(&p.kcount[t], 1u);
+            const int last = old == static_cast<unsigned int>(nsplit - 1);
+            if (last) p.kcount[t] = 0u;          // everybody has arrived: zero again for the next launch on this slot
+            *s_last = last;
+          }
+          asm volatile("bar.sync 1, %0;" ::"r"(128 * parts) : "memory");
+          if (*s_last) {
+            __threadfence();
+            const float4* first = reinterpret_cast<const float4*>(p.kpart) + static_cast<int64_t>(t) * nsplit * (BN_T / 4) * BM + row;
+            epilogue_rows_from_partials<BN_T>(valid ? first : nullptr, nsplit, static_cast<int64_t>(BN_T / 4) * BM, p,
+                                              valid ? p.out + dst_row * p.ldo : nullptr, tc.nt * BN_T, part, parts,
+                                              smem + TSTAGES * TSTAGE_BYTES + 256 + (warp - 2) * 4096, lane);
+          }
+          continue;
+        }
+      }
       if constexpr (epi_glu(EPI))
         epilogue_glu_staged<EPI, BN_T>(taddr, p, valid ? dst_row * p.ldo : -1ll, tc.nt * (BN_T / 2), part,
                                        epilogue_parts(), smem + TSTAGES * TSTAGE_BYTES + 256 + (warp - 2) * 2048, lane);
@@ -1674,7 +1801,7 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
     return b_mn ? go(routed_gemm_pair_kernel<A_MODE, EPI, OUT_MODE, true>)
                 : go(routed_gemm_pair_kernel<A_MODE, EPI, OUT_MODE, false>);
   }
-  int64_t grid = ((M + BM - 1) / BM + 1) * n_tiles;
+  int64_t grid = ((M + BM - 1) / BM + 1) * n_tiles * (p.ksplit > 1 ? p.ksplit : 1);
   if (grid > usable_sms(dev)) grid = usable_sms(dev);
   if (grid < 1) grid = 1;
   auto go = [&](auto kernel) -> int {
@@ -1825,9 +1952,77 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
                     : launch_gemm<A_GATHER, EPI_SWIGLU, OUT_SCATTER>(tmA, tmB, mn, p, M, tile, s);
 }
 
-extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
-                             int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy,
-                             int64_t M, int64_t d, int64_t h, int32_t* status, void* stream) {
+// Split-K plan of the down projection for few row tiles.  One tcgen05.mma of 128 rows takes about 128
+// cycles however narrow its N is, so a CTA that walks all of K = h alone issues h/16 of them in a row
+// (h = 2816: 22 k cycles, most of the kernel's time at 127 tokens) while most SMs have no tile.  With the
+// contraction cut into `splits` ranges the chain shrinks by that factor; the price is a round trip of fp32
+// partial tiles through L2, a counter per tile and the last arrival's pass over `splits` partial tiles.
+// Estimate in cycles for a tile width bn and a number of ranges (one wave only: the items must fit the SMs):
+//   k-steps per item x 505 (four MMAs a k-step) + 400 + 85 x bn + 0.2 x items x bn for the exchange
+// (the last arrival reads the partial tiles sixteen columns a round, so narrow tiles are what makes the
+// exchange cheap), fitted to graph-replayed forwards at d = 1024, h = 2816, 127 tokens: no split 33.7 us;
+// 64-column tiles in 2 / 4 ranges 31.2 / 28.3; 128-column tiles in 4 ranges 31.4; 256-column 38.0.  Other
+// points: 256 tokens 33.8 -> 29.9, 384 tokens 36.6 -> 33.6, from 500 tokens on nothing is gained; d = 2048,
+// h = 8192, 127 tokens 77.7 -> 60.5; d = 4096, h = 11008, 64 tokens 146 -> 134.  A split is taken when its
+// estimate is below 0.85 of the unsplit chain.
+struct SplitKPlan {
+  int bn = 0;        // 0: no split-K (the table's own tile)
+  int splits = 1;
+};
+
+static SplitKPlan down_splitk_plan(int64_t M, int64_t d, int64_t h, bool k_major) {
+  SplitKPlan plan;
+  const int forced = tune_overrides().ksplit;
+  if (!k_major || forced == 0 || forced == 1 || M >= 4096 || tune_overrides().pair > 0) return plan;
+  const int sms = usable_sms(device_info());
+  const int64_t m_tiles = (M + BM - 1) / BM + 1;
+  const int64_t k_steps = (h + BK - 1) / BK;
+  int64_t best = k_steps * 505 * 85 / 100;
+  for (int bn : {64, 128, 256}) {
+    const int64_t tiles = m_tiles * ((d + bn - 1) / bn);
+    if (tiles > kSplitKTiles) continue;
+    for (int sp = 2; sp <= kMaxSplitK; ++sp) {
+      if (tiles * sp > sms || k_steps / sp < (forced > 1 ? 1 : 4)) break;
+      if (forced > 1 && sp != (forced > kMaxSplitK ? kMaxSplitK : forced)) continue;
+      const int64_t est = (k_steps + sp - 1) / sp * 505 + 400 + 85 * bn + tiles * sp * bn / 5;
+      if (est < best || (forced > 1 && plan.splits <= 1)) {
+        best = est;
+        plan = SplitKPlan{bn, sp};
+      }
+    }
+  }
+  return plan;
+}
+
+namespace ffnk {
+int64_t ffn_down_scratch_bytes(int64_t M, int64_t d, int64_t h) {
+  // the plan may differ with the weights' layout; reserve for the K-major one (the other never splits)
+  const SplitKPlan pl = down_splitk_plan(M, d, h, true);
+  if (pl.splits <= 1) return 0;
+  const int64_t tiles = ((M + BM - 1) / BM + 1) * ((d + pl.bn - 1) / pl.bn);
+  return tiles * pl.splits * BM * pl.bn * static_cast<int64_t>(sizeof(float));
+}
+}  // namespace ffnk
+
+// the device address of the split-K counters, looked up once per process
+static int splitk_counters(unsigned int** out) {
+  static unsigned int* cached = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_splitk_count);
+    if (e != cudaSuccess) return cuda_status(e);
+    cached = static_cast<unsigned int*>(ptr);
+  }
+  *out = cached;
+  return 0;
+}
+
+int ffnk::ffn_down_with_scratch(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
+                                int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy,
+                                int64_t M, int64_t d, int64_t h, void* scratch, int64_t scratch_bytes, int32_t* status,
+                                void* stream) {
   if (M == 0) return 0;
   if (!inter || !w2 || !u2 || !perm || !counts || !y) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
@@ -1840,14 +2035,37 @@ extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, con
   for (int i = 0; i <= COPY_MAP; ++i)
       if (i != RUN_LEVELS) tmA.m[i] = tmA.m[RUN_LEVELS];
   bool mn1 = false, mn2 = false;
-  const TileChoice tile = pick_tile(M, d, A_ROUTED, EPI_STORE, weights_k_major(w_stride_k, w_stride_n, h));
+  const bool k_major = weights_k_major(w_stride_k, w_stride_n, h);
+  TileChoice tile = pick_tile(M, d, A_ROUTED, EPI_STORE, k_major);
+  SplitKPlan pl;
+  if (scratch && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0) {
+    pl = down_splitk_plan(M, d, h, k_major);
+    if (pl.splits > 1 && ffn_down_scratch_bytes(M, d, h) <= scratch_bytes) tile = TileChoice{false, pl.bn};
+    else pl = SplitKPlan{};
+  }
   if ((r = weight_map(&tmB[0], WeightView{w2, w_stride_k, w_stride_n, h, d}, &mn1, tile.bn / 2))) return r;
   if ((r = weight_map(&tmB[2], WeightView{u2, w_stride_k, w_stride_n, h, d}, &mn2, tile.bn / 2))) return r;
   tmB[1] = tmB[0];
   tmB[3] = tmB[2];
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(y), ldy, static_cast<int>(d), static_cast<int>(h),
                static_cast<int>(M), pick_group_m(h), max_run_rows(), status, g_prof_buffer};
+  if (pl.splits > 1) {
+    unsigned int* counters = nullptr;
+    if ((r = splitk_counters(&counters))) return r;
+    static unsigned launch_seq = 0;   // successive launches take successive rows of counters
+    const unsigned slot = __atomic_fetch_add(&launch_seq, 1u, __ATOMIC_RELAXED) % kSplitKSlots;
+    p.ksplit = pl.splits;
+    p.kpart = static_cast<float*>(scratch);
+    p.kcount = counters + static_cast<size_t>(slot) * kSplitKTiles;
+  }
   return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
+                             int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy,
+                             int64_t M, int64_t d, int64_t h, int32_t* status, void* stream) {
+  return ffn_down_with_scratch(inter, ldi, w2, u2, w_stride_k, w_stride_n, perm, counts, y, ldy, M, d, h, nullptr, 0,
+                               status, stream);
 }
 
 extern "C" int ffnk_ffn_down_to_peers(const void* inter, int64_t ldi, const void* w2, const void* u2,

@@ -266,10 +266,20 @@ def test_full_size_rows_sampled(dev):
 def test_single_call_and_step_by_step_paths_agree(dev, M):
     from ffn_kernel_b200 import route
     c = ffn_case(M, 256, 520, seed=M, mask=edge_mask(M, "bernoulli", 4)).to(dev)
-    y_one = _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)
+    from ffn_kernel_b200._lib import lib
+    L = lib()
+    # the single call may split the down projection's contraction (another summation order): switched off, the
+    # two paths launch the same kernels and give the same bits; switched on, they agree to rounding
+    assert L.ffnk_tune_override(b"ksplit", 0) == 0
+    try:
+        y_one = _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)
+    finally:
+        assert L.ffnk_tune_override(b"ksplit", -1) == 0
     y_steps = _bf16_ffn_fused_forward(*c.apply_args(), rt=route(c.mask), allow_decode=False)
+    y_auto = _bf16_ffn_fused_forward(*c.apply_args(), allow_decode=False)
     check_status()
     assert torch.equal(y_one, y_steps)
+    assert O.max_rel_err(y_auto, y_steps.float().cpu()) < 5e-3
 
 
 @pytest.mark.parametrize("M", [1, 8])
@@ -297,3 +307,46 @@ def test_single_call_rejects_a_short_workspace(dev):
                             c.u2.data_ptr(), c.u3.data_ptr(), 1, d, 1, h, c.mask.data_ptr(), ws.data_ptr(), need - 256,
                             y.data_ptr(), d, M, d, h, 1, status_word(dev).data_ptr(), stream_ptr(dev))
     assert rc == -8
+
+
+@pytest.mark.parametrize("M", [81, 127, 129, 1000, 2047])
+@pytest.mark.parametrize("kind", ["all_visual", "alternating", "bernoulli", "span"])
+@pytest.mark.parametrize("splits", [0, 2, 4])
+def test_down_projection_split_over_the_contraction(dev, M, kind, splits):
+    # few row tiles: the single-call forward may cut the down projection's contraction into ranges whose
+    # fp32 partial tiles are added in a fixed order by the last range to finish; forced off (0) and on
+    # (2, 8) here: every choice agrees with the oracle and gives the same bits twice
+    from ffn_kernel_b200._lib import lib
+    L = lib()
+    d, h = 1024, 2816
+    c = ffn_case(M, d, h, seed=M, mask=edge_mask(M, kind, seed=M))
+    ref = O.masked_ffn(*c.apply_args())
+    g = c.to(dev)
+    assert L.ffnk_tune_override(b"ksplit", splits) == 0
+    try:
+        with torch.no_grad():
+            y = MaskedFFN.apply(*g.apply_args())
+            y2 = MaskedFFN.apply(*g.apply_args())
+        check_status()
+    finally:
+        assert L.ffnk_tune_override(b"ksplit", -1) == 0
+    assert O.max_rel_err(y, ref) < TOL
+    assert torch.equal(y, y2)
+
+
+def test_down_projection_split_ragged_shape(dev):
+    from ffn_kernel_b200._lib import lib
+    L = lib()
+    M, d, h = 300, 264, 1096            # d not a multiple of a column tile, h not a multiple of a k-step
+    c = ffn_case(M, d, h, seed=3, mask=edge_mask(M, "bernoulli", seed=5))
+    ref = O.masked_ffn(*c.apply_args())
+    g = c.to(dev)
+    for splits in (0, 4):
+        assert L.ffnk_tune_override(b"ksplit", splits) == 0
+        try:
+            with torch.no_grad():
+                y = MaskedFFN.apply(*g.apply_args())
+            check_status()
+        finally:
+            assert L.ffnk_tune_override(b"ksplit", -1) == 0
+        assert O.max_rel_err(y, ref) < TOL
