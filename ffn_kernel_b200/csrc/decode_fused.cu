@@ -385,19 +385,34 @@ using namespace ffnk;
 extern "C" int ffnk_decode_max_tokens(void) { return kDecodeTableTokens; }
 
 // Tile-table entry: does a forward of M tokens take this kernel?  Both paths stream the weights once; this
-// one adds the token rows that every CTA re-reads from L2 for each of its units (as many bytes as the
-// weights at 16 tokens per modality), the GEMM path adds about 25 us of fixed cost (routing, permutation
-// and two GEMM launches with their pipeline fill).  Fitted to measurements with both modalities present
-// (a = microseconds the weights take at 3.9 TB/s):
-//     decode(M) = (a + 6 us) * (1 + (M - 8) / 60),   gemm = 1.114 * a + 25 us
-// d=1024/h=2816 (a = 8.9): decode 14.9 us at 8 tokens, 28.7 at 64, 35.4 at 96; GEMM path 37: break-even
-// near 88.  d=4096/h=11008 (a = 139): decode 0.142 ms at 8 tokens, 0.292 at 64; GEMM path 0.154 at 96:
-// break-even near 22 tokens.
+// one adds the token rows that every CTA re-reads from L2 for each of its units, the GEMM path (routing and
+// row copy in one launch, gate/up GEMM, split-K down projection) has a fixed cost of some 18 us but little
+// that grows with M.  Fitted to graph-replayed forwards with both modalities present (a = microseconds the
+// weights take at 3.9 TB/s):
+//     decode(M) = (a + 6 us) * (1 + (max(M, 8) - 8) / 60)
+//     gemm(a)   = through the measured points (a, us): (1.6, 19.7) (3.2, 22.5) (8.9, 27.0) (51.6, 55.7) (138.7, 133)
+// d=1024/h=2816 (a = 8.9): decode 14.8 us at 8 tokens, 23.7 at 56, 28.6 at 64; GEMM path 27-28.5 from 8 to 127
+// tokens: break-even near 57.  d=512/h=1024: decode 12.8 us at 80 tokens, GEMM path 20.  d=2048/h=8192 and
+// d=4096/h=11008: the GEMM path is ahead from two tokens on (55 against 59 us, 131 against 138 us at 4
+// tokens: 0.62 against 0.58 of the HBM peak).  A single token has one modality and half the weights: this
+// kernel (31.6 against 50.3 us, 76 against 89 us).
+static double gemm_path_us(double a) {
+  static const double pts[][2] = {{1.6, 19.7}, {3.2, 22.5}, {8.9, 27.0}, {51.6, 55.7}, {138.7, 133.0}};
+  constexpr int n = sizeof(pts) / sizeof(pts[0]);
+  if (a <= pts[0][0]) return pts[0][1];
+  for (int i = 1; i < n; ++i)
+    if (a <= pts[i][0])
+      return pts[i - 1][1] + (pts[i][1] - pts[i - 1][1]) * (a - pts[i - 1][0]) / (pts[i][0] - pts[i - 1][0]);
+  return pts[n - 1][1] * a / pts[n - 1][0];
+}
+
 extern "C" int ffnk_ffn_takes_decode(int64_t M, int64_t d, int64_t h) {
   if (M < 1 || M > kDecodeTableTokens || d < 8 || h < 8) return 0;
+  if (M == 1) return 1;
   const double a = 12.0 * static_cast<double>(d) * static_cast<double>(h) / 3.9e6;
-  const double limit = 8.0 + 60.0 * (0.114 * a + 19.0) / (a + 6.0);
-  return static_cast<double>(M) <= limit ? 1 : 0;
+  const double m_eff = M < 8 ? 8.0 : static_cast<double>(M);
+  const double decode_us = (a + 6.0) * (1.0 + (m_eff - 8.0) / 60.0);
+  return decode_us <= gemm_path_us(a) ? 1 : 0;
 }
 extern "C" int ffnk_decode_capacity(void) { return kFusedMaxTokens; }
 

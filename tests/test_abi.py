@@ -47,10 +47,12 @@ def test_pure_host_functions(libffnk):
 
 
 def test_decode_table_entry(libffnk):
-    # up to 80 tokens at the small FFN, fewer the wider the FFN, never beyond the kernel's capacity; monotone in M
+    # up to 80 tokens at small FFNs, about 57 at d=1024/h=2816, a single token at wide FFNs (the GEMM path with
+    # its split-K down projection is ahead there); never beyond the kernel's capacity; monotone in M
     L = libffnk
     assert L.ffnk_decode_max_tokens() == 80 and L.ffnk_decode_capacity() == 127
-    for d, h, lo, hi in ((1024, 2816, 80, 80), (4096, 11008, 16, 32), (256, 520, 80, 80)):
+    for d, h, lo, hi in ((1024, 2816, 50, 64), (4096, 11008, 1, 1), (2048, 8192, 1, 1), (256, 520, 80, 80),
+                         (512, 1024, 80, 80)):
         takes = [bool(L.ffnk_ffn_takes_decode(M, d, h)) for M in range(0, 130)]
         limit = max(M for M, t in enumerate(takes) if t)
         assert lo <= limit <= hi, (d, h, limit)
