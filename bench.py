@@ -415,10 +415,13 @@ def named_configs(b: Bench) -> dict:
         with torch.no_grad():
             fns = [(lambda cs=cs: MaskedFFN.apply(x, *cs.apply_args()[1:7], mask)) for cs in cases]
             ms = graph_replay_ms(fns)
+        from ffn_kernel_b200.ffn import takes_decode
+        path = "one-launch decode kernel" if takes_decode(Mx, d, h) else "routing + row copy, gate/up GEMM, down GEMM"
         if Mx <= 127:
-            c5[f"m{Mx}"] = hbm_entry(ms, present * 3.0 * d * h * 2 + 2.0 * Mx * d * 2, modalities_present=present)
+            c5[f"m{Mx}"] = hbm_entry(ms, present * 3.0 * d * h * 2 + 2.0 * Mx * d * 2, modalities_present=present,
+                                     path=path)
         else:
-            c5[f"m{Mx}"] = tensor_entry(ms, 6.0 * Mx * d * h)
+            c5[f"m{Mx}"] = tensor_entry(ms, 6.0 * Mx * d * h, path=path)
     out["c5_ffn_fwd_d1024_h2816"] = c5
     del cases
 
