@@ -272,6 +272,12 @@ int ffnk_ffn_decode(const void* x, int64_t ldx, const void* w1, const void* w2, 
  * the caller and reusable as soon as the stream has passed this call; too small a workspace
  * returns FFNK_ERR_CAPACITY.  ffnk_ffn_permute_first() tells whether the tile table copies x
  * into routed order first for this shape.
+ * With few row tiles (up to 384 tokens at d = 1024, h = 2816) the down projection cuts its contraction
+ * into ranges on different SMs; their arrival counters are this library's own, one row of counters per
+ * launch in turn over 64 rows, each left at zero by the launch that used it: the barrier-counter rule
+ * of ffnk_ffn_decode applies (no more than 64 such launches in flight on one device at a time; a
+ * captured launch keeps the row it was captured with).  The result does not depend on which range
+ * finishes last (the partial tiles are added in a fixed order).
  * ------------------------------------------------------------------------------------- */
 int64_t ffnk_ffn_workspace_bytes(int64_t M, int64_t d, int64_t h);
 int ffnk_ffn_permute_first(int64_t M, int64_t d, int64_t h);
