@@ -6,6 +6,9 @@
     python -m ffn_kernel_b200.sweep decode   --M 8 --d 1024 --h 2816 [--mask alternating]
     FFNK_PAIR=1 python -m ffn_kernel_b200.sweep waits --M 16384 --d 4096 --h 11008
         (wait-cycle counters of the CTA-pair GEMM kernels: who waits for whom, and the SM clock)
+    python -m ffn_kernel_b200.sweep paths    --d 1024 --h 2816 --tokens 8,32,64,127,256
+        (small token counts: the decode kernel, the GEMM path and the GEMM path without its split-K down
+         projection, each as one library call replayed from a CUDA graph over rotated weight sets)
 
 Each kernel is launched through the C ABI and timed with CUDA events on the launching stream
 (warm-up first, inputs larger than L2 or rotated over several copies).  One JSON line per kernel.
@@ -49,7 +52,8 @@ def emit(**kw):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["ffn", "linear", "route", "decode", "once", "waits"])
+    ap.add_argument("what", choices=["ffn", "linear", "route", "decode", "once", "waits", "paths"])
+    ap.add_argument("--tokens", default="8,32,64,127,256", help="paths: token counts, comma separated")
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--d", type=int, default=4096)
     ap.add_argument("--h", type=int, default=11008)
@@ -64,6 +68,51 @@ def main():
     dev = torch.device("cuda", torch.cuda.current_device())
     L = lib()
     st, sp = status_word(dev).data_ptr(), stream_ptr(dev)
+
+    if a.what == "paths":
+        # The table entries for small token counts, measured: every path as the single library call,
+        # replayed from a CUDA graph that visits enough weight sets to overflow L2 (so each call streams
+        # its weights from HBM), Bernoulli(0.5) mask unless --mask says otherwise.
+        d, h = a.d, a.h
+        kind = "bernoulli" if a.mask == "span" else a.mask
+        sets = max(2, min(6, int(200e6 // (12 * d * h)) + 1))
+        capacity = int(L.ffnk_decode_capacity())
+
+        def replay_us(fns):
+            for fn in fns:
+                fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for fn in fns:
+                    fn()
+            return timeit(g.replay, a.iters, a.warmup) / len(fns) * 1e3
+
+        def decode_call(cs, M, inter, y):
+            L.ffnk_ffn_decode(cs.x.data_ptr(), d, cs.w1.data_ptr(), cs.w2.data_ptr(), cs.w3.data_ptr(), cs.u1.data_ptr(),
+                              cs.u2.data_ptr(), cs.u3.data_ptr(), 1, d, 1, h, cs.mask.data_ptr(), inter.data_ptr(),
+                              y.data_ptr(), d, M, d, h, st, stream_ptr(dev))   # the stream current now (the capture's)
+
+        for M in [int(t) for t in a.tokens.split(",") if t]:
+            cases = [ffn_case(M, d, h, seed=100 + i, mask=edge_mask(M, kind, seed=M)).to(dev) for i in range(sets)]
+            row = dict(kernel="ffn_forward paths", M=M, d=d, h=h, mask=kind, weight_sets=sets,
+                       table_takes_decode=bool(L.ffnk_ffn_takes_decode(M, d, h)))
+            with torch.no_grad():
+                if M <= capacity:
+                    inter = torch.empty((M, h), device=dev, dtype=torch.bfloat16)
+                    y = torch.empty((M, d), device=dev, dtype=torch.bfloat16)
+                    row["decode_us"] = replay_us([(lambda cs=cs: decode_call(cs, M, inter, y)) for cs in cases])
+                gemm = [(lambda cs=cs: _bf16_ffn_fused_forward(*cs.apply_args(), allow_decode=False)) for cs in cases]
+                row["gemm_us"] = replay_us(gemm)
+                L.ffnk_tune_override(b"ksplit", 0)
+                try:
+                    row["gemm_no_splitk_us"] = replay_us(gemm)
+                finally:
+                    L.ffnk_tune_override(b"ksplit", -1)
+            check_status()
+            emit(**{k: (round(v, 2) if isinstance(v, float) else v) for k, v in row.items()})
+            del cases
+        return
 
     if a.what == "waits" and a.bwd:
         # weight-gradient kernel of the MaskedLinear backward: who waits for whom
