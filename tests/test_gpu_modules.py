@@ -66,3 +66,17 @@ def test_graphed_ffn_replays_match_eager(dev, tokens):
     with pytest.raises(RuntimeError):
         graphed(torch.zeros(tokens + 1, 256, device=dev, dtype=torch.bfloat16),
                 torch.zeros(tokens + 1, device=dev, dtype=torch.bool))
+
+
+def test_sweep_paths_tool_runs(dev, monkeypatch, capsys):
+    # the tool behind the decode table entry: one JSON line per token count with the three paths' times
+    import json
+    import sys
+    from ffn_kernel_b200 import sweep
+    monkeypatch.setattr(sys, "argv", ["sweep", "paths", "--d", "256", "--h", "520", "--tokens", "8,200", "--iters", "2",
+                                      "--warmup", "1"])
+    sweep.main()
+    rows = [json.loads(ln) for ln in capsys.readouterr().out.strip().splitlines()]
+    assert [r["M"] for r in rows] == [8, 200]
+    assert rows[0]["decode_us"] > 0 and rows[0]["gemm_us"] > 0 and rows[0]["gemm_no_splitk_us"] > 0
+    assert "decode_us" not in rows[1] and rows[1]["gemm_us"] > 0        # beyond the decode kernel's capacity
