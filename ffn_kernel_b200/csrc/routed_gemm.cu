@@ -446,13 +446,16 @@ template <int BN_T>
 __device__ __forceinline__ void epilogue_rows_from_partials(const float4* src, int nsplit, int64_t stride, const GemmParams& p,
                                                            __nv_bfloat16* dst, int n_base, int part, int parts,
                                                            uint8_t* stg, int lane) {
+  // With two warps per lane quarter (parts == 2) each takes half of every 64-column chunk: 32 columns = two
+  // groups of sixteen, stored as 64 contiguous bytes per row, eight rows per instruction.
   constexpr int CH = BN_T / 64;
   const unsigned long long dptr = reinterpret_cast<unsigned long long>(dst);
-  const int piece = lane & 7;
+  const int lanes_per_row = 8 / parts;                       // 16-byte pieces of a row this warp stores
+  const int piece = (lane & (lanes_per_row - 1)) + part * lanes_per_row;
 #pragma unroll 1
-  for (int c = part * CH / parts; c < (part + 1) * CH / parts; ++c) {
+  for (int c = 0; c < CH; ++c) {
 #pragma unroll 1
-    for (int jp = 0; jp < 4; ++jp) {
+    for (int jp = part * 4 / parts; jp < (part + 1) * 4 / parts; ++jp) {
       float4 t[kMaxSplitK][4];
 #pragma unroll
       for (int sp = 0; sp < kMaxSplitK; ++sp) {
@@ -484,9 +487,9 @@ __device__ __forceinline__ void epilogue_rows_from_partials(const float4* src, i
     }
     __syncwarp();
     const int n0 = n_base + c * 64 + piece * 8;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = i * 4 + (lane >> 3);
+    const int rows_per_store = 32 / lanes_per_row;
+    for (int i = 0; i < lanes_per_row; ++i) {
+      const int r = i * rows_per_store + lane / lanes_per_row;
       const unsigned long long rp = __shfl_sync(0xFFFFFFFFu, dptr, r);
       const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128 + ((piece ^ (r & 7)) << 4));
       if (rp != 0ull && n0 < p.n_out) *reinterpret_cast<uint4*>(rp + static_cast<unsigned long long>(n0) * 2ull) = val;
@@ -1807,7 +1810,9 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
   auto go = [&](auto kernel) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM + extra_smem);
     if (e != cudaSuccess) return cuda_status(e);
-    kernel<<<static_cast<unsigned>(grid), gemm_threads_for(static_cast<int64_t>(p.k_len) + p.k_len1), GEMM_SMEM + extra_smem, stream>>>(
+    // a split contraction is short per item and ends in a pass over the partial tiles: eight epilogue warps
+    const int threads = p.ksplit > 1 ? GEMM_THREADS_MAX : gemm_threads_for(static_cast<int64_t>(p.k_len) + p.k_len1);
+    kernel<<<static_cast<unsigned>(grid), threads, GEMM_SMEM + extra_smem, stream>>>(
         tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
     return cuda_status(cudaGetLastError());
   };
