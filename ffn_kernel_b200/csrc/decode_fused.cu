@@ -390,14 +390,14 @@ extern "C" int ffnk_decode_max_tokens(void) { return kDecodeTableTokens; }
 // that grows with M.  Fitted to graph-replayed forwards with both modalities present (a = microseconds the
 // weights take at 3.9 TB/s):
 //     decode(M) = (a + 6 us) * (1 + (max(M, 8) - 8) / 60)
-//     gemm(a)   = through the measured points (a, us): (1.6, 19.7) (3.2, 22.5) (8.9, 27.0) (51.6, 55.7) (138.7, 133)
+//     gemm(a)   = through the measured points (a, us): (1.6, 19.7) (3.2, 22.5) (8.9, 27.0) (51.6, 55.7) (138.7, 124)
 // d=1024/h=2816 (a = 8.9): decode 14.8 us at 8 tokens, 23.7 at 56, 28.6 at 64; GEMM path 27-28.5 from 8 to 127
 // tokens: break-even near 57.  d=512/h=1024: decode 12.8 us at 80 tokens, GEMM path 20.  d=2048/h=8192 and
-// d=4096/h=11008: the GEMM path is ahead from two tokens on (55 against 59 us, 131 against 138 us at 4
-// tokens: 0.62 against 0.58 of the HBM peak).  A single token has one modality and half the weights: this
+// d=4096/h=11008: the GEMM path is ahead from two tokens on (8 tokens: 53 against 58 us, 124 against 139 us:
+// 0.67 against 0.59 of the HBM peak).  A single token has one modality and half the weights: this
 // kernel (31.6 against 50.3 us, 76 against 89 us).
 static double gemm_path_us(double a) {
-  static const double pts[][2] = {{1.6, 19.7}, {3.2, 22.5}, {8.9, 27.0}, {51.6, 55.7}, {138.7, 133.0}};
+  static const double pts[][2] = {{1.6, 19.7}, {3.2, 22.5}, {8.9, 27.0}, {51.6, 55.7}, {138.7, 124.0}};
   constexpr int n = sizeof(pts) / sizeof(pts[0]);
   if (a <= pts[0][0]) return pts[0][1];
   for (int i = 1; i < n; ++i)

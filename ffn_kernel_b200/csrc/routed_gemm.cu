@@ -1759,7 +1759,19 @@ static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool 
   for (int bn : {256, 128, 64}) {
     const int64_t n_per_tile = epi_glu(epi) ? bn / 2 : bn;
     const int64_t tiles = m_tiles * ((n_out + n_per_tile - 1) / n_per_tile);
-    const int64_t est = ((tiles + sms - 1) / sms) * (16384 + 128 * bn);
+    int64_t est = ((tiles + sms - 1) / sms) * (16384 + 128 * bn);
+    if (epi_glu(epi) && M <= BM) {
+      // One row tile per modality: the token rows come out of L2 and the weights are what streams.  In SM
+      // units of one tile's bytes: full waves cost the number of SMs each, a last wave of r tiles costs
+      // max(r, SMs / 2) (an SM alone pulls about twice its share of the HBM rate, no more); and however
+      // narrow the tile, a CTA issues four MMAs of about 128 cycles per k-step, which bounds the narrowest
+      // tiles (d=4096, h=11008, 8 tokens: 256 columns 85 us, 128 columns 79 us, 64 columns 105 us;
+      // d=1024, h=2816, 127 tokens: 17.0 / 15.2 / 20.1 us).
+      const int64_t full = tiles / sms, rest = tiles % sms;
+      const int64_t stream = (full * sms + (rest == 0 ? 0 : (2 * rest > sms ? rest : sms / 2))) * (4096 + 128 * bn);
+      const int64_t issue = ((tiles + sms - 1) / sms) * sms * 12288;
+      est = stream > issue ? stream : issue;
+    }
     if (best < 0 || est < best) {
       best = est;
       t.bn = bn;
