@@ -2245,9 +2245,14 @@ extern "C" int ffnk_ffn_forward_train(const void* x, int64_t ldx, const void* w1
   for (const void* q : al)
     if (reinterpret_cast<uintptr_t>(q) & 15) return FFNK_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int r = ffnk_route(mask, M, perm, counts, scan_workspace, status, stream);
-  if (r) return r;
-  if ((r = ffnk_permute_rows(x, ldx, perm, counts, xr, d, M, d, stream))) return r;
+  int r;
+  if (M <= ffnk_route_permute_max_tokens()) {
+    // a mask of one routing tile: routing and the row copy are one launch
+    if ((r = ffnk_route_permute_rows(mask, M, x, ldx, d, perm, counts, xr, d, stream))) return r;
+  } else {
+    if ((r = ffnk_route(mask, M, perm, counts, scan_workspace, status, stream))) return r;
+    if ((r = ffnk_permute_rows(x, ldx, perm, counts, xr, d, M, d, stream))) return r;
+  }
   const int64_t rows = ffnk_route_capacity(M) + 512;
   {
     AMaps tmA;
