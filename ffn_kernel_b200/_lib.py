@@ -101,10 +101,10 @@ def lib() -> ctypes.CDLL:
 
 # Tile-table overrides for measurements (`python -m ffn_kernel_b200.tune`, the forced-variant test runs):
 # FFNK_PAIR, FFNK_NARROW, FFNK_PERMUTE, FFNK_EPI_WARPS, FFNK_GROUP_M, FFNK_WGRAD_PAIR, FFNK_MAX_RUN_ROWS,
-# FFNK_COPY_THRESHOLD, FFNK_VERBOSE, FFNK_ROUTE_RESIDENT, FFNK_KSPLIT are read HERE, once, and handed to the library through
+# FFNK_COPY_THRESHOLD, FFNK_VERBOSE, FFNK_ROUTE_RESIDENT, FFNK_KSPLIT, FFNK_EARLY_START are read HERE, once, and handed to the library through
 # ffnk_tune_override; the library itself never looks at the environment.
 _ENV_OVERRIDES = ("pair", "narrow", "permute", "epi_warps", "group_m", "wgrad_pair", "max_run_rows",
-                  "copy_threshold", "verbose", "route_resident", "ksplit")
+                  "copy_threshold", "verbose", "route_resident", "ksplit", "early_start")
 
 
 def _apply_env_overrides(handle) -> None:

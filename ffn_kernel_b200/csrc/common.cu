@@ -130,7 +130,7 @@ extern "C" int ffnk_tune_override(const char* name, int value) {
       {"pair", &t.pair}, {"narrow", &t.narrow}, {"permute", &t.permute}, {"epi_warps", &t.epi_warps},
       {"group_m", &t.group_m}, {"wgrad_pair", &t.wgrad_pair}, {"max_run_rows", &t.max_run_rows},
       {"copy_threshold", &t.copy_threshold}, {"verbose", &t.verbose}, {"route_resident", &t.route_resident},
-      {"ksplit", &t.ksplit}};
+      {"ksplit", &t.ksplit}, {"early_start", &t.early_start}};
   for (auto& e : table)
     if (strcmp(e.n, name) == 0) {
       *e.v = value;

@@ -96,9 +96,12 @@ extern "C" int ffnk_ffn_forward(const void* x, int64_t ldx, const void* w1, cons
   } else if ((r = ffnk_route(mask, M, perm, counts, ws + w.scan, status, stream))) {
     return r;
   }
-  if ((r = ffnk_ffn_gateup(a, lda, w1, w3, u1, u3, w13_stride_k, w13_stride_n, perm, counts, ws + w.inter, h,
-                           routed_in, 1, M, d, h, status, stream)))
+  // Few row tiles leave most SMs idle: the two GEMMs are launched so that each may set itself up and ask its
+  // weights into L2 while its predecessor still runs (programmatic dependent launch; single-CTA tiles only).
+  const int early = M < 4096 && tune_overrides().early_start != 0 ? 1 : 0;
+  if ((r = ffn_gateup_early(a, lda, w1, w3, u1, u3, w13_stride_k, w13_stride_n, perm, counts, ws + w.inter, h, routed_in,
+                            1, M, d, h, early, status, stream)))
     return r;
   return ffn_down_with_scratch(ws + w.inter, h, w2, u2, w2_stride_k, w2_stride_n, perm, counts, y, ldy, M, d, h,
-                               w.kpart_bytes ? ws + w.kpart : nullptr, w.kpart_bytes, status, stream);
+                               w.kpart_bytes ? ws + w.kpart : nullptr, w.kpart_bytes, early, status, stream);
 }

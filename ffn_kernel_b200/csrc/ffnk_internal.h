@@ -45,6 +45,7 @@ struct TuneOverrides {
   int verbose = -1;         // 1: print the arguments of a tensor map the driver rejects
   int route_resident = -1;  // 0: long masks never take the one-launch resident routing kernel (count + scatter instead)
   int ksplit = -1;          // down projection of the FFN forward: 0/1 never split K, n > 1 split n ways wherever it can
+  int early_start = -1;     // 0: the GEMMs of the single-call FFN forward never start beside their predecessor
 };
 TuneOverrides& tune_overrides();
 
@@ -54,9 +55,16 @@ long long* debug_profile_buffer();
 // ffnk_ffn_down with an optional scratch buffer (16-byte aligned) for the fp32 partial tiles of its split-K
 // variant, which it takes for few row tiles when ffn_down_scratch_bytes(M, d, h) > 0 bytes are given.
 int64_t ffn_down_scratch_bytes(int64_t M, int64_t d, int64_t h);
+// early != 0 (single-CTA tiles only): the kernel is launched so that it may start beside its predecessor in
+// the stream (programmatic dependent launch) and ask its weights into L2 until the predecessor has finished.
 int ffn_down_with_scratch(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
                           int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy, int64_t M,
-                          int64_t d, int64_t h, void* scratch, int64_t scratch_bytes, int32_t* status, void* stream);
+                          int64_t d, int64_t h, void* scratch, int64_t scratch_bytes, int early, int32_t* status,
+                          void* stream);
+int ffn_gateup_early(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1, const void* u3,
+                     int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* out,
+                     int64_t ldo, int routed_in, int routed_out, int64_t M, int64_t d, int64_t h, int early,
+                     int32_t* status, void* stream);
 
 // permute_rows with an optional device-side gate: with only_if_scattered = T > 0 the kernel returns at
 // once unless the mask's runs of same-modality tokens average fewer than T rows.

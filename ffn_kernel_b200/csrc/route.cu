@@ -731,6 +731,7 @@ __global__ void __launch_bounds__(kRouteThreads) route_permute_kernel(const uint
   __shared__ int s_warp[kRouteThreads / 32];
   __shared__ int s_runs;
   const int tid = threadIdx.x;
+  griddep_launch_dependents();         // the GEMM behind this kernel may set itself up and ask its weights into L2
   const ThreadTokens tt = load_thread_tokens(mask, M, tid * kRoutePerThread);
   if (tid == 0) s_runs = 0;
   int Mv = 0;

@@ -111,6 +111,15 @@ struct GemmParams {
   int ksplit = 1;
   float* kpart = nullptr;
   unsigned int* kcount = nullptr;
+  // Early start (single CTAs): pdl != 0 says the kernel was launched with the programmatic-stream-
+  // serialization attribute, i.e. it may be running beside its predecessor in the stream.  Until
+  // griddep_wait() it touches nothing the predecessor writes; what it does meanwhile, besides its set-up,
+  // is ask the weights (up to four matrices of pf_rows rows of pf_row_bytes bytes, pf_stride bytes apart)
+  // into L2, every CTA its share.
+  int pdl = 0;
+  const char* pf_base[4] = {nullptr, nullptr, nullptr, nullptr};
+  int64_t pf_stride = 0;
+  int pf_rows = 0, pf_row_bytes = 0;
 };
 
 // Split-K arrival counters, one row of kSplitKTiles per launch in turn (launches that could overlap on the
@@ -544,10 +553,28 @@ routed_gemm_kernel(const __grid_constant__ AMaps am, const __grid_constant__ CUt
     tmem_alloc<1>(tmem_slot, TMEM_COLS);
     tmem_relinquish<1>();
   }
+  // a dependent kernel may start its own set-up now (this kernel's CTAs are all resident or done)
+  griddep_launch_dependents();
+  if (p.pdl) {
+    // weights into L2 while the predecessor (routing and row copy, or the gate/up GEMM) is still running
+    const int lines_per_row = (p.pf_row_bytes + 127) >> 7;
+    const int64_t lines = static_cast<int64_t>(p.pf_rows) * lines_per_row;
+#pragma unroll 1
+    for (int w = 0; w < 4; ++w) {
+      if (p.pf_base[w] == nullptr) continue;
+      for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < lines;
+           i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / lines_per_row;
+        const int l = static_cast<int>(i - r * lines_per_row);
+        prefetch_l2(p.pf_base[w] + r * p.pf_stride + min(l * 128, p.pf_row_bytes - 1));
+      }
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  griddep_wait();                       // from here on the predecessor's results (lists, counts, activations) are read
 
   const int Mv = p.counts[0], Mt = p.counts[1], cap = p.counts[2];
   const int tiles_v = (Mv + BM - 1) / BM;
@@ -1782,6 +1809,20 @@ static TileChoice pick_tile(int64_t M, int64_t n_out, int a_mode, int epi, bool 
 
 static bool weights_k_major(int64_t stride_k, int64_t stride_n, int64_t K) { return stride_k == 1 && stride_n >= K; }
 
+// Early start of a single-CTA GEMM behind its predecessor (GemmParams::pdl), with up to four K-major
+// weights [rows, row_elems] to ask into L2 meanwhile; more than 64 MiB of weights are not prefetched
+// (they would push one another out of L2 again).
+static void early_start(GemmParams& p, const void* const* weights, int nweights, int64_t rows, int64_t row_elems,
+                        int64_t stride_elems, bool k_major) {
+  p.pdl = 1;
+  if (!k_major || nweights * rows * row_elems * 2 > (int64_t(64) << 20) || rows >= (1ll << 30) || row_elems >= (1ll << 29))
+    return;
+  for (int i = 0; i < nweights && i < 4; ++i) p.pf_base[i] = static_cast<const char*>(weights[i]);
+  p.pf_stride = stride_elems * 2;
+  p.pf_rows = static_cast<int>(rows);
+  p.pf_row_bytes = static_cast<int>(row_elems * 2);
+}
+
 template <int A_MODE, int EPI, int OUT_MODE>
 static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn, const GemmParams& p,
                        int64_t M, TileChoice tile, cudaStream_t stream) {
@@ -1824,6 +1865,19 @@ static int launch_gemm(const AMaps& tmA, const CUtensorMap (&tmB)[4], bool b_mn,
     if (e != cudaSuccess) return cuda_status(e);
     // a split contraction is short per item and ends in a pass over the partial tiles: eight epilogue warps
     const int threads = p.ksplit > 1 ? GEMM_THREADS_MAX : gemm_threads_for(static_cast<int64_t>(p.k_len) + p.k_len1);
+    if (p.pdl) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(grid));
+      cfg.blockDim = dim3(threads);
+      cfg.dynamicSmemBytes = GEMM_SMEM + extra_smem;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      return cuda_status(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB[0], tmB[1], tmB[2], tmB[3], p));
+    }
     kernel<<<static_cast<unsigned>(grid), threads, GEMM_SMEM + extra_smem, stream>>>(
         tmA, tmB[0], tmB[1], tmB[2], tmB[3], p);
     return cuda_status(cudaGetLastError());
@@ -1935,6 +1989,14 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
                                const void* u3, int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm,
                                const int32_t* counts, void* out, int64_t ldo, int routed_in, int routed_out, int64_t M,
                                int64_t d, int64_t h, int32_t* status, void* stream) {
+  return ffn_gateup_early(x, ldx, w1, w3, u1, u3, w_stride_k, w_stride_n, perm, counts, out, ldo, routed_in, routed_out, M, d,
+                          h, 0, status, stream);
+}
+
+int ffnk::ffn_gateup_early(const void* x, int64_t ldx, const void* w1, const void* w3, const void* u1, const void* u3,
+                           int64_t w_stride_k, int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* out,
+                           int64_t ldo, int routed_in, int routed_out, int64_t M, int64_t d, int64_t h, int early,
+                           int32_t* status, void* stream) {
   if (M == 0) return 0;
   if (!x || !w1 || !w3 || !u1 || !u3 || !perm || !counts || !out) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
@@ -1961,6 +2023,7 @@ extern "C" int ffnk_ffn_gateup(const void* x, int64_t ldx, const void* w1, const
   }
   GemmParams p{perm, counts, static_cast<__nv_bfloat16*>(out), ldo, static_cast<int>(h), static_cast<int>(d),
                static_cast<int>(M), pick_group_m(d), max_run_rows(), status, g_prof_buffer};
+  if (early && !tile.pair) early_start(p, ws, 4, h, d, w_stride_n, weights_k_major(w_stride_k, w_stride_n, d));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (routed_in)
     return routed_out ? launch_gemm<A_ROUTED, EPI_SWIGLU, OUT_ROUTED>(tmA, tmB, mn, p, M, tile, s)
@@ -2038,8 +2101,8 @@ static int splitk_counters(unsigned int** out) {
 
 int ffnk::ffn_down_with_scratch(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
                                 int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy,
-                                int64_t M, int64_t d, int64_t h, void* scratch, int64_t scratch_bytes, int32_t* status,
-                                void* stream) {
+                                int64_t M, int64_t d, int64_t h, void* scratch, int64_t scratch_bytes, int early,
+                                int32_t* status, void* stream) {
   if (M == 0) return 0;
   if (!inter || !w2 || !u2 || !perm || !counts || !y) return FFNK_ERR_NULL;
   if (M < 0 || M >= (1ll << 30) || bad_dim(d) || bad_dim(h)) return FFNK_ERR_SHAPE;
@@ -2075,13 +2138,17 @@ int ffnk::ffn_down_with_scratch(const void* inter, int64_t ldi, const void* w2, 
     p.kpart = static_cast<float*>(scratch);
     p.kcount = counters + static_cast<size_t>(slot) * kSplitKTiles;
   }
+  if (early && !tile.pair) {
+    const void* ws2[2] = {w2, u2};
+    early_start(p, ws2, 2, d, h, w_stride_n, k_major);
+  }
   return launch_gemm<A_ROUTED, EPI_STORE, OUT_SCATTER>(tmA, tmB, mn1, p, M, tile, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ffnk_ffn_down(const void* inter, int64_t ldi, const void* w2, const void* u2, int64_t w_stride_k,
                              int64_t w_stride_n, const int32_t* perm, const int32_t* counts, void* y, int64_t ldy,
                              int64_t M, int64_t d, int64_t h, int32_t* status, void* stream) {
-  return ffn_down_with_scratch(inter, ldi, w2, u2, w_stride_k, w_stride_n, perm, counts, y, ldy, M, d, h, nullptr, 0,
+  return ffn_down_with_scratch(inter, ldi, w2, u2, w_stride_k, w_stride_n, perm, counts, y, ldy, M, d, h, nullptr, 0, 0,
                                status, stream);
 }
 

@@ -340,7 +340,8 @@ int ffnk_debug_profile_buffer(void* buffer);
  * find_spec/find.py:18-64).  name: "pair", "narrow", "permute", "epi_warps", "group_m", "wgrad_pair",
  * "max_run_rows", "copy_threshold", "verbose", "route_resident" (0: long masks are routed by the count and
  * scatter kernels even where the one-launch kernel fits), "ksplit" (down projection inside ffnk_ffn_forward: 0 never
- * splits the contraction, n > 1 splits it n ways wherever it can); value -1 restores the table's own choice.  Process-wide,
+ * splits the contraction, n > 1 splits it n ways wherever it can), "early_start" (0: the GEMMs inside
+ * ffnk_ffn_forward never start beside their predecessor); value -1 restores the table's own choice.  Process-wide,
  * affects later launches; unknown names return FFNK_ERR_SHAPE.  The library reads no environment variables. */
 int ffnk_tune_override(const char* name, int value);
 

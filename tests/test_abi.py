@@ -62,7 +62,7 @@ def test_decode_table_entry(libffnk):
 def test_tune_override_names(libffnk):
     L = libffnk
     for name in (b"pair", b"narrow", b"permute", b"epi_warps", b"group_m", b"wgrad_pair", b"max_run_rows",
-                 b"copy_threshold", b"verbose", b"route_resident", b"ksplit"):
+                 b"copy_threshold", b"verbose", b"route_resident", b"ksplit", b"early_start"):
         assert L.ffnk_tune_override(name, -1) == 0
     assert L.ffnk_tune_override(b"no_such_entry", 1) < 0
     assert L.ffnk_tune_override(None, 1) < 0
