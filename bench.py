@@ -581,9 +581,12 @@ def run_ours(args):
     probe_rows = (rows_dp.stop - rows_dp.start) if mode == "dp" else M
     chunks_in_step = {"fused_broadcast_2chunks": 2, "fused_broadcast_4chunks": 4}.get(variant_name, 1)
     phase_events = []
+    # events made ahead of the timed region: creating one costs the host several microseconds, which shows in
+    # a step of 0.8 ms that Python launches kernel by kernel
+    event_pool = [torch.cuda.Event(enable_timing=True) for _ in range(8 * steps * chunks_in_step + 8)]
 
     def hook(name):
-        ev = torch.cuda.Event(enable_timing=True)
+        ev = event_pool.pop() if event_pool else torch.cuda.Event(enable_timing=True)
         ev.record()
         phase_events.append((name, ev))
 
